@@ -1,0 +1,348 @@
+"""Benchmark of the MoE layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at N=1 (the decode sweep the headline metric is quoted on): one OLMoE-1B-7B MoE layer
+(hidden 2048, 64 experts of width 1024, top-8, no renormalisation) in fp16 on the
+weight-streaming path, at T = 1, 8, 32 and 64 tokens. A step is one pass of the layer at each
+T. Every pass runs on a different layer's weights (LAYERS weight sets are resident and used
+in rotation), so a pass never finds its weights in L2.
+
+  value   expert-weight GB/s: bytes of the expert weights the passes had to read (experts that
+          received a row x 3*H*I*2 bytes, the reference's bench/kernels.py formula) / time of
+          the whole layer passes (router GEMM to combine), inputs resident in HBM, each pass
+          replayed from a CUDA graph;
+  e2e     the same through the public Python API with HOST buffers: hidden states copied from
+          pinned memory, `kernels.moe_layer`, result copied back, every pass;
+  roofline the dominant kernel (the SwiGLU weight stream of T=64) alone: algorithmic bytes per
+          launch / its CUDA-event duration, against the measured HBM copy bandwidth;
+  cpu_baseline / --impl reference: the float32 expert loop of the CPU oracle on the same
+          sweep, on the host cores.
+
+Prints ONE JSON line on rank 0."""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SWEEP = (1, 8, 32, 64)
+H, I, E, TOPK = 2048, 1024, 64, 8
+EXPERT_BYTES = 3 * H * I * 2          # fp16 bytes of one expert's weights
+GATE_UP_BYTES = 2 * H * I * 2
+LAYERS = 8                             # resident weight sets used in rotation (8 x 805 MB)
+METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.p = index, None
+
+    def __enter__(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                      stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.p.terminate()
+        try:
+            out, _ = self.p.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+            out, _ = self.p.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_sweep_inputs(seed=0):
+    """float32 weights and hidden states of the sweep on the host (same distributions)."""
+    g = torch.Generator().manual_seed(seed)
+    router = torch.randn(E, H, generator=g) * 0.02
+    gate_up = torch.randn(E, 2 * I, H, generator=g) * 0.02
+    down = torch.randn(E, H, I, generator=g) * 0.02
+    hs = {T: torch.randn(T, H, generator=g) for T in SWEEP}
+    return router, gate_up, down, hs
+
+
+def cpu_sweep_once(mo, router, gate_up, down, hs):
+    """One sweep of the float32 reference loop; returns (seconds, algorithmic fp16 bytes)."""
+    total_bytes, t0 = 0, time.perf_counter()
+    for T in SWEEP:
+        idx, w = mo.route_reference(hs[T], router, TOPK, False)
+        mo.experts_reference(hs[T], idx, w, gate_up, down)
+        total_bytes += int(torch.unique(idx).numel()) * EXPERT_BYTES
+    return time.perf_counter() - t0, total_bytes
+
+
+def cpu_leg(sweeps, warmup=1):
+    from oracle import moe_oracle as mo
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    router, gate_up, down, hs = cpu_sweep_inputs()
+    for _ in range(warmup):
+        cpu_sweep_once(mo, router, gate_up, down, hs)
+    times, nbytes = [], 0
+    for _ in range(sweeps):
+        dt, nbytes = cpu_sweep_once(mo, router, gate_up, down, hs)
+        times.append(dt)
+    return times, nbytes, torch.get_num_threads()
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU implementation of the path (its float32 expert
+    loop, restated in oracle/moe_oracle.py) on the host cores, one sweep per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times, nbytes, threads = cpu_leg(args.steps, args.warmup)
+    total = sum(times)
+    value = nbytes * len(times) / total / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(times) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1] decode sweep T=1,8,32,64 on the host: float32 reference expert loop",
+                   "tokens": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{len(times)} sweeps of T=1,8,32,64, float32, torch CPU"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def run_single_gpu(args):
+    from switchyard_b200 import kernels, synthetic
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    kernels.ext()
+    dtype = torch.float16
+    layers = [synthetic.layer_weights(dev, dtype, seed=100 + l) for l in range(LAYERS)]
+    hs = {T: synthetic.hidden_states(T, dev, dtype, seed=T) for T in SWEEP}
+    mode = "gemv"
+
+    # experts used per (T, layer): fixed by the seeds, needed for the byte count
+    used = {}
+    for T in SWEEP:
+        for l, (router, _, _) in enumerate(layers):
+            idx, _ = kernels.route(hs[T], router, TOPK, False)
+            used[(T, l)] = int(torch.unique(idx).numel())
+    torch.cuda.synchronize()
+
+    # one CUDA graph per (T, layer): the whole layer, router GEMM to combine
+    stream = torch.cuda.Stream(dev)
+    graphs, outs = {}, {}
+    with torch.cuda.stream(stream):
+        for T in SWEEP:
+            for l, (router, gu, dn) in enumerate(layers):
+                for _ in range(2):
+                    kernels.moe_layer(hs[T], router, gu, dn, TOPK, False, mode)
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    outs[(T, l)] = kernels.moe_layer(hs[T], router, gu, dn, TOPK, False, mode)
+                graphs[(T, l)] = g
+    torch.cuda.synchronize()
+    assert kernels.ext().device_status(dev) == 0
+
+    per_T_ms = {T: 0.0 for T in SWEEP}
+    per_T_bytes = {T: 0 for T in SWEEP}
+    pass_no = [0]
+
+    def step(timed):
+        evs = []
+        for T in SWEEP:
+            l = pass_no[0] % LAYERS
+            pass_no[0] += 1
+            if timed:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+            graphs[(T, l)].replay()
+            if timed:
+                b.record(stream)
+                evs.append((T, l, a, b))
+        return evs
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step(False)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(dev.index).__enter__()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        all_evs = []
+        t0.record(stream)
+        for _ in range(args.steps):
+            all_evs += step(True)
+        t1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    total_ms = t0.elapsed_time(t1)
+    total_bytes = 0
+    for T, l, a, b in all_evs:
+        per_T_ms[T] += a.elapsed_time(b)
+        per_T_bytes[T] += used[(T, l)] * EXPERT_BYTES
+        total_bytes += used[(T, l)] * EXPERT_BYTES
+    value = total_bytes / (total_ms / 1e3) / 1e9
+    sweep = [{"tokens": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
+              "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
+              "experts_used_mean": per_T_bytes[T] / EXPERT_BYTES / args.steps} for T in SWEEP]
+
+    # ---- end to end through the public API with host buffers
+    host_in = {T: hs[T].cpu().pin_memory() for T in SWEEP}
+    host_out = {T: torch.empty(T, H, dtype=dtype).pin_memory() for T in SWEEP}
+    dev_in = {T: torch.empty_like(hs[T]) for T in SWEEP}
+
+    def e2e_step():
+        nbytes = 0
+        for T in SWEEP:
+            l = pass_no[0] % LAYERS
+            pass_no[0] += 1
+            router, gu, dn = layers[l]
+            dev_in[T].copy_(host_in[T], non_blocking=True)
+            out = kernels.moe_layer(dev_in[T], router, gu, dn, TOPK, False, mode)
+            host_out[T].copy_(out, non_blocking=True)
+            nbytes += used[(T, l)] * EXPERT_BYTES
+        torch.cuda.current_stream().synchronize()  # the results are on the host
+        return nbytes
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            e2e_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        e2e_bytes = sum(e2e_step() for _ in range(args.steps))
+        e1.record(stream)
+        torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    io_bytes = sum(T * H * 2 for T in SWEEP)
+
+    # ---- the dominant kernel alone: SwiGLU weight stream of T=64, one launch per layer in rotation
+    T = SWEEP[-1]
+    ext = kernels.ext()
+    kern_ms, kern_bytes = [], []
+    with torch.cuda.stream(stream):
+        sorted_in = []
+        for l, (router, gu, dn) in enumerate(layers):
+            idx, w = kernels.route(hs[T], router, TOPK, False)
+            counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, E)
+            sorted_in.append((token, offsets))
+        for rep in range(max(args.steps, 8) + 3):
+            l = rep % LAYERS
+            token, offsets = sorted_in[l]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            ext.grouped_gemv(hs[T], token, layers[l][1], offsets, T * TOPK, True, None)
+            b.record(stream)
+            stream.synchronize()
+            if rep >= 3:
+                kern_ms.append(a.elapsed_time(b))
+                kern_bytes.append(used[(T, l)] * GATE_UP_BYTES)
+    peak, peak_src = peaks()
+    achieved = sum(kern_bytes) / (sum(kern_ms) / 1e3) / 1e9
+    assert ext.device_status(dev) == 0
+
+    # ---- CPU baseline (bounded sample of the same sweep)
+    cpu_times, cpu_bytes, threads = cpu_leg(sweeps=20, warmup=1)
+    cpu_value = cpu_bytes * len(cpu_times) / sum(cpu_times) / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "configs[1]: OLMoE MoE layer decode sweep T=1,8,32,64, fp16, grouped_gemv path; "
+                               "a step = one layer pass at each T",
+                   "tokens": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK, "mode": mode,
+                   "l2": f"inputs larger than L2: passes rotate over {LAYERS} resident weight sets of 805 MB",
+                   "timing": "CUDA events on the launch stream around CUDA-graph replays of the whole layer",
+                   "seeds": {"weights": "100+layer", "hidden": "T"}},
+        "sweep": sweep,
+        "vs_nominal_8TBps": value / 8000.0,
+        "clocks": clocks,
+        "e2e": {"value": e2e_bytes / (e2e_ms / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
+                "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms / args.steps,
+                "api": "switchyard_b200.kernels.moe_layer, eager, host buffers pinned"},
+        "gpu_launches": args.steps * len(SWEEP) * 5,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "kernel": "gemv_stream_kernel<half, SWIGLU>",
+                     "workload": "T=64 gate/up projection, one launch per layer in rotation",
+                     "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
+                     "vs_nominal_8TBps": achieved / 8000.0},
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{len(cpu_times)} sweeps of T=1,8,32,64, float32 expert loop (oracle), torch CPU",
+                         "ms_per_sweep": statistics.median(cpu_times) * 1e3},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        sys.exit("bench.py needs a CUDA GPU (there is no CPU path); use --impl reference for the CPU baseline")
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return run_single_gpu(args)
+    from switchyard_b200 import bench_ep
+    return bench_ep.run(args)
+
+
+if __name__ == "__main__":
+    main()

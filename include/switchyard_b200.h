@@ -1,0 +1,117 @@
+/* switchyard_b200 — C ABI of the sm_100a mixture-of-experts kernels.
+ *
+ * Every entry point takes raw device pointers, sizes, a 16-bit element type and a CUDA
+ * stream (passed as void*; it is a cudaStream_t). Nothing here allocates, frees, synchronises
+ * the device or takes ownership: outputs and scratch are the caller's, inputs are borrowed
+ * until the enqueued work has run. Calls are asynchronous on `stream`, on the CURRENT device,
+ * and may be made concurrently from several host threads (one per device).
+ *
+ * Return value: SY_OK (0) or a negative SY_ERR_* code; sy_last_error() gives the message of
+ * the calling thread's last failure.
+ *
+ * Each declaration names the entry point of the reference project's extension that it
+ * replaces (file:line in the reference's tree, switchyard/csrc/moe_kernels.cu).
+ */
+#ifndef SWITCHYARD_B200_H
+#define SWITCHYARD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SY_OK 0
+#define SY_ERR_ARGUMENT (-1) /* a shape, alignment or limit check failed; nothing was enqueued */
+#define SY_ERR_CUDA (-2)     /* a CUDA runtime / driver call failed */
+#define SY_ERR_DEVICE (-3)   /* a kernel gave up on a bounded wait (see sy_device_status) */
+
+#define SY_DTYPE_F16 0
+#define SY_DTYPE_BF16 1
+
+/* Message of the calling thread's last failing call ("" if none). Never NULL. */
+const char* sy_last_error(void);
+
+/* Library version string. */
+const char* sy_version(void);
+
+/* Blocks until `stream` is idle, then returns the current device's kernel status word and
+ * clears it: 0, or the DeviceStatus code of the first bounded wait that gave up. Only tests
+ * and error paths need it. */
+int sy_device_status(void* stream, int* status_out);
+
+/* route — replaces `route` (moe_kernels.cu:73-89, kernel l.23-71).
+ * logits [n_tokens, n_experts] row-major, 16-bit. One warp per token: float32 softmax,
+ * top_k rounds of arg-max with ties to the lower expert index, optional renormalisation.
+ * idx_out int32 [n_tokens, top_k] (descending probability), w_out 16-bit [n_tokens, top_k].
+ * Limits: n_experts <= 128, top_k <= 8, top_k <= n_experts. n_tokens == 0 is a no-op. */
+int sy_route(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
+             int32_t* idx_out, void* w_out, void* stream);
+
+/* Scratch bytes sy_sort_by_expert needs for m choices (0 when one block sorts everything). */
+size_t sy_sort_scratch_bytes(int m, int n_experts);
+
+/* sort_by_expert — replaces `sort_by_expert` (moe_kernels.cu:142-157, kernels l.94-139 and the
+ * torch cumsum between them). Stable counting sort of the flat choice list (i = token*top_k +
+ * slot) by expert id, no atomics, same result every run.
+ * idx int32 [m] (m = n_tokens*top_k, values in [0, n_experts)), w 16-bit [m].
+ * Outputs: counts int32 [n_experts]; offsets int32 [n_experts+1] (exclusive prefix);
+ * token int32 [m] (= i / top_k of the choice in that sorted row); wsorted 16-bit [m];
+ * pos_of int32 [m] (sorted row of choice i). m == 0 zero-fills counts and offsets.
+ * scratch: sy_sort_scratch_bytes(m, n_experts) bytes of device memory (may be NULL if 0).
+ * Limit: n_experts <= 256. */
+int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n_experts, int dtype,
+                      int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                      void* scratch, size_t scratch_bytes, void* stream);
+
+/* grouped_gemv — replaces `grouped_gemv` (moe_kernels.cu:385-415, kernel l.306-383).
+ * For every sorted row r of expert e (offsets[e] <= r < offsets[e+1]):
+ *   C[r, :] = A[src(r), :] . B[e]^T,  src(r) = a_rows ? a_rows[r] : r
+ * A 16-bit [*, k_dim]; B 16-bit [n_experts, n_full, k_dim] (nn.Linear layout per expert),
+ * n_full = swiglu ? 2*n_out (gate rows first, then up rows) : n_out; C 16-bit [rows, n_out].
+ * swiglu: C = silu(gate) * up with 16-bit rounding after each step; scale (16-bit [rows], may
+ * be NULL, not with swiglu): C = round16(acc) * scale[r]. Accumulation is float32 in a fixed
+ * order per row, so a row's bits do not depend on which other rows share its expert.
+ * The decode path: a persistent weight stream, bulk-async copies into shared memory.
+ * Requirements: k_dim % 8 == 0, n_out % 8 == 0, 16-byte aligned A, B; n_experts <= 256. */
+int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
+                    int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
+                    int dtype, void* stream);
+
+/* grouped_gemm — replaces `grouped_gemm` (moe_kernels.cu:264-298, kernel l.159-261) and the
+ * host-side `tile_offsets` / `total_tiles` arguments, which this implementation does not need:
+ * work is scheduled on the device from `offsets`. Same contraction and epilogues as
+ * sy_grouped_gemv, computed on the tcgen05 tensor cores with accumulators in tensor memory,
+ * expert weights fed by TMA and activation rows gathered from A in-kernel.
+ * Requirements: k_dim % 64 == 0, n_out % 64 == 0, 16-byte aligned A, 128-byte aligned B. */
+int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
+                    int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
+                    int dtype, void* stream);
+
+/* combine — replaces `combine` (moe_kernels.cu:435-444, kernel l.417-433).
+ * out[t, :] = round16( sum_j float(y[pos_of[t*top_k + order_j], :]) ), the token's top_k rows
+ * added in ascending expert id (ties in slot order), float32 accumulation, one rounding.
+ * y 16-bit [m, hidden]; pos_of int32 [m]; idx int32 [n_tokens, top_k]; out 16-bit
+ * [n_tokens, hidden]. hidden % 8 == 0, top_k <= 8. */
+int sy_combine(const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
+               void* out, int dtype, void* stream);
+
+/* gather_rows — replaces `gather_rows` (moe_kernels.cu:459-467, kernel l.450-457).
+ * dst[row, :] = src[index[row], :] for row < n; row_bytes % 16 == 0. dst may be memory of a
+ * peer GPU (peer access enabled, or an IPC mapping): the dispatch store. */
+int sy_gather_rows(const void* src, const int32_t* index, int n, int row_bytes, void* dst, void* stream);
+
+/* copy_async — replaces `copy_async` (moe_kernels.cu:470-475): contiguous copy between any
+ * two device buffers (same GPU or peers) on `stream`. */
+int sy_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+
+/* enable_peer_access — replaces `enable_peer_access` (moe_kernels.cu:477-489). Sets
+ * *enabled_out to 1 if `device` can (now) address `peer`'s memory, 0 if the hardware cannot.
+ * Already-enabled is not an error. */
+int sy_enable_peer_access(int device, int peer, int* enabled_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWITCHYARD_B200_H */

@@ -1,0 +1,113 @@
+// route: router logits -> float32 softmax -> top-k experts and weights. One warp per token.
+//
+// Arithmetic contract (what makes the expert indices bit-exact against the reference kernel,
+// switchyard/csrc/moe_kernels.cu:23-71): expert e lives in lane e % 32, register e / 32; the
+// maximum and the sum of exp(v - max) are float32 xor-butterflies; selection runs on the exp
+// values, larger first and the LOWER expert index on equal values; weights are exp / sum,
+// divided by the sum of the picked weights when renormalising, rounded once to 16 bits.
+#include "common.cuh"
+
+namespace sy {
+
+constexpr int ROUTE_THREADS = 256;
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int norm, int* __restrict__ idx,
+             T* __restrict__ w) {
+  const int lane = threadIdx.x & 31;
+  const int token = (blockIdx.x * ROUTE_THREADS + threadIdx.x) >> 5;
+  if (token >= n_tokens) return;
+  const T* row = logits + (size_t)token * E;
+
+  float v[PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    int e = lane + 32 * j;
+    v[j] = e < E ? Elem<T>::to_f(row[e]) : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    int e = lane + 32 * j;
+    v[j] = e < E ? expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+
+  // k rounds of warp arg-max; lane r keeps round r's pick so that the stores are coalesced
+  float my_w = 0.f, total = 0.f;
+  int my_e = 0;
+  for (int r = 0; r < k; ++r) {
+    float best = -1.f;
+    int best_e = 1 << 30;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      int e = lane + 32 * j;
+      if (e < E && (v[j] > best || (v[j] == best && e < best_e))) {
+        best = v[j];
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j)
+      if (lane + 32 * j == best_e) v[j] = -1.f;  // taken
+    float p = best / sum;
+    total += p;
+    if (lane == r) {
+      my_w = p;
+      my_e = best_e;
+    }
+  }
+  if (lane < k) {
+    idx[(size_t)token * k + lane] = my_e;
+    w[(size_t)token * k + lane] = Elem<T>::from_f(norm ? my_w / total : my_w);
+  }
+}
+
+template <typename T>
+static int launch_route(const void* logits, int n_tokens, int E, int k, int norm, int32_t* idx, void* w,
+                        cudaStream_t stream) {
+  int blocks = (n_tokens * 32 + ROUTE_THREADS - 1) / ROUTE_THREADS;
+  const T* l = static_cast<const T*>(logits);
+  T* wp = static_cast<T*>(w);
+  if (E <= 32)
+    route_kernel<T, 1><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
+  else if (E <= 64)
+    route_kernel<T, 2><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
+  else
+    route_kernel<T, 4><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
+  return check_cuda(cudaGetLastError(), "route launch");
+}
+
+}  // namespace sy
+
+extern "C" int sy_route(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
+                        int32_t* idx_out, void* w_out, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_tokens >= 0, "route: negative token count");
+  SY_REQUIRE(n_experts >= 1 && n_experts <= 128 && top_k >= 1 && top_k <= 8 && top_k <= n_experts,
+             "route: at most 128 experts and top-8 (got E=%d, k=%d)", n_experts, top_k);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "route: dtype must be f16 or bf16");
+  if (n_tokens == 0) return SY_OK;
+  SY_REQUIRE(logits && idx_out && w_out, "route: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == SY_DTYPE_F16
+             ? launch_route<__half>(logits, n_tokens, n_experts, top_k, norm_topk_prob, idx_out, w_out, s)
+             : launch_route<__nv_bfloat16>(logits, n_tokens, n_experts, top_k, norm_topk_prob, idx_out, w_out, s);
+}

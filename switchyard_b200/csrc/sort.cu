@@ -1,0 +1,255 @@
+// sort_by_expert: stable counting sort of the flat (token, choice) list by expert id.
+//
+// Deterministic and free of atomics. The list is cut into contiguous chunks, one per block,
+// and each chunk into contiguous pieces, one per warp; a warp walks its piece 32 choices at a
+// time. Inside a 32-wide step, __match_any_sync groups the lanes that hold the same expert, a
+// lane's rank in its group is the number of lower lanes in it, and the group's lowest lane
+// advances the warp's private per-expert counter in shared memory. Ranks therefore follow
+// increasing flat index, which is exactly the order a stable sort gives.
+//
+//   one block  (m <= SORT_SINGLE_MAX): count, scan and scatter in a single launch;
+//   many blocks: launch 1 writes per-block expert counts to scratch [blocks][E]; launch 2
+//                re-counts its own chunk per warp, turns the scratch table into its starting
+//                row per expert, and scatters. Two reads of 4 bytes per choice in total.
+//
+// Replaces the reference's one-block-per-expert sort (switchyard/csrc/moe_kernels.cu:94-157),
+// which reads the whole list once per expert and calls torch for the prefix sum in between.
+#include "common.cuh"
+
+namespace sy {
+
+constexpr int SORT_THREADS = 512;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int SORT_MAX_E = 256;
+constexpr int SORT_SINGLE_MAX = 8192;       // choices one block sorts by itself
+constexpr int SORT_CHUNK = 4096;            // target choices per block when several blocks sort
+constexpr int SORT_MAX_BLOCKS = 128;        // scratch table rows that launch 2 keeps in shared memory
+
+struct SortShape {
+  int blocks;      // blocks of the grid
+  int per_block;   // choices per block (multiple of 32 * SORT_WARPS)
+};
+
+static SortShape sort_shape(int m) {
+  SortShape s;
+  if (m <= SORT_SINGLE_MAX) {
+    s.blocks = 1;
+    s.per_block = ((m + SORT_THREADS - 1) / SORT_THREADS) * SORT_THREADS;
+    return s;
+  }
+  int blocks = (m + SORT_CHUNK - 1) / SORT_CHUNK;
+  if (blocks > SORT_MAX_BLOCKS) blocks = SORT_MAX_BLOCKS;
+  int per = (m + blocks - 1) / blocks;
+  per = ((per + SORT_THREADS - 1) / SORT_THREADS) * SORT_THREADS;
+  s.blocks = (m + per - 1) / per;
+  s.per_block = per;
+  return s;
+}
+
+// Per-warp expert counts of this block's chunk into wcount[warp][e] (shared, zeroed here).
+__device__ __forceinline__ void count_chunk(const int* __restrict__ idx, int m, int begin, int per_warp, int E,
+                                            int* wcount) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < SORT_WARPS * E; i += SORT_THREADS) wcount[i] = 0;
+  __syncthreads();
+  int* mine = wcount + warp * E;
+  const int start = begin + warp * per_warp;
+  for (int base = start; base < start + per_warp && base < m; base += 32) {
+    int i = base + lane;
+    int e = i < m ? idx[i] : -1;
+    bool ok = e >= 0 && e < E;
+    unsigned group = __match_any_sync(0xffffffffu, ok ? e : -1);
+    if (ok && lane == __ffs(group) - 1) mine[e] += __popc(group);
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+// Exclusive scan of v[0..E) by one warp, result in out[0..E], out[E] = total. E <= SORT_MAX_E.
+__device__ __forceinline__ void warp_scan_experts(const int* v, int E, int* out) {
+  const int lane = threadIdx.x & 31;
+  int carry = 0;
+  for (int base = 0; base < E; base += 32) {
+    int e = base + lane;
+    int x = e < E ? v[e] : 0, inc = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += y;
+    }
+    if (e < E) out[e] = carry + inc - x;
+    carry += __shfl_sync(0xffffffffu, inc, 31);
+  }
+  if (lane == 0) out[E] = carry;
+}
+
+template <typename T>
+__device__ __forceinline__ void scatter_chunk(const int* __restrict__ idx, const T* __restrict__ w, int m, int k,
+                                              int begin, int per_warp, int E, int* wbase,
+                                              int* __restrict__ token, T* __restrict__ wsorted,
+                                              int* __restrict__ pos_of, int* status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* mine = wbase + warp * E;
+  const int start = begin + warp * per_warp;
+  for (int base = start; base < start + per_warp && base < m; base += 32) {
+    int i = base + lane;
+    int e = i < m ? idx[i] : -1;
+    bool ok = e >= 0 && e < E;
+    if (i < m && !ok) *status = DS_BAD_INDEX;  // an expert id outside [0, E): the row is skipped
+    unsigned group = __match_any_sync(0xffffffffu, ok ? e : -1);
+    int pos = 0;
+    if (ok) pos = mine[e] + __popc(group & ((1u << lane) - 1u));
+    __syncwarp();
+    if (ok && lane == __ffs(group) - 1) mine[e] += __popc(group);
+    __syncwarp();
+    if (ok) {
+      token[pos] = i / k;
+      wsorted[pos] = w[i];
+      pos_of[i] = pos;
+    }
+  }
+}
+
+// One block does everything.
+template <typename T>
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_single_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, int k, int E, int per_block,
+                   int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ token,
+                   T* __restrict__ wsorted, int* __restrict__ pos_of, int* status) {
+  extern __shared__ int sh[];
+  int* wcount = sh;                       // [SORT_WARPS][E]
+  int* total = wcount + SORT_WARPS * E;   // [E]
+  int* off = total + E;                   // [E + 1]
+  const int per_warp = per_block / SORT_WARPS;
+  count_chunk(idx, m, 0, per_warp, E, wcount);
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int s = 0;
+    for (int wi = 0; wi < SORT_WARPS; ++wi) s += wcount[wi * E + e];
+    total[e] = s;
+    counts[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) warp_scan_experts(total, E, off);
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
+  // wcount[warp][e] <- first row of warp's rows of expert e
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int at = off[e];
+    for (int wi = 0; wi < SORT_WARPS; ++wi) {
+      int c = wcount[wi * E + e];
+      wcount[wi * E + e] = at;
+      at += c;
+    }
+  }
+  __syncthreads();
+  scatter_chunk<T>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
+}
+
+// Launch 1 of the multi-block sort: this block's expert counts into table[block][e].
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_count_kernel(const int* __restrict__ idx, int m, int E, int per_block, int* __restrict__ table) {
+  extern __shared__ int sh[];
+  int* wcount = sh;
+  count_chunk(idx, m, blockIdx.x * per_block, per_block / SORT_WARPS, E, wcount);
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int s = 0;
+    for (int wi = 0; wi < SORT_WARPS; ++wi) s += wcount[wi * E + e];
+    table[blockIdx.x * E + e] = s;
+  }
+}
+
+// Launch 2: starting rows from the table, then the stable scatter of this block's chunk.
+template <typename T>
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_scatter_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, int k, int E, int per_block,
+                    const int* __restrict__ table, int* __restrict__ counts, int* __restrict__ offsets,
+                    int* __restrict__ token, T* __restrict__ wsorted, int* __restrict__ pos_of, int* status) {
+  extern __shared__ int sh[];
+  int* wcount = sh;                       // [SORT_WARPS][E]
+  int* total = wcount + SORT_WARPS * E;   // [E]
+  int* off = total + E;                   // [E + 1]
+  int* before = off + E + 1;              // [E] rows of expert e in earlier blocks
+  const int per_warp = per_block / SORT_WARPS;
+  count_chunk(idx, m, blockIdx.x * per_block, per_warp, E, wcount);
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int s = 0, b4 = 0;
+    for (int b = 0; b < (int)gridDim.x; ++b) {
+      int c = table[b * E + e];
+      if (b < (int)blockIdx.x) b4 += c;
+      s += c;
+    }
+    total[e] = s;
+    before[e] = b4;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) warp_scan_experts(total, E, off);
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < E; e += SORT_THREADS) counts[e] = total[e];
+    for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
+  }
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int at = off[e] + before[e];
+    for (int wi = 0; wi < SORT_WARPS; ++wi) {
+      int c = wcount[wi * E + e];
+      wcount[wi * E + e] = at;
+      at += c;
+    }
+  }
+  __syncthreads();
+  scatter_chunk<T>(idx, w, m, k, blockIdx.x * per_block, per_warp, E, wcount, token, wsorted, pos_of, status);
+}
+
+template <typename T>
+static int launch_sort(const int32_t* idx, const void* w, int m, int k, int E, int32_t* counts, int32_t* offsets,
+                       int32_t* token, void* wsorted, int32_t* pos_of, void* scratch, cudaStream_t stream) {
+  SortShape s = sort_shape(m);
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  size_t smem = (size_t)(SORT_WARPS * E + 3 * E + 1) * sizeof(int);
+  const T* wp = static_cast<const T*>(w);
+  T* ws = static_cast<T*>(wsorted);
+  if (s.blocks == 1) {
+    sort_single_kernel<T><<<1, SORT_THREADS, smem, stream>>>(idx, wp, m, k, E, s.per_block, counts, offsets, token,
+                                                             ws, pos_of, status);
+  } else {
+    int* table = static_cast<int*>(scratch);
+    sort_count_kernel<<<s.blocks, SORT_THREADS, (size_t)SORT_WARPS * E * sizeof(int), stream>>>(idx, m, E, s.per_block,
+                                                                                             table);
+    sort_scatter_kernel<T><<<s.blocks, SORT_THREADS, smem, stream>>>(idx, wp, m, k, E, s.per_block, table, counts,
+                                                                    offsets, token, ws, pos_of, status);
+  }
+  return check_cuda(cudaGetLastError(), "sort launch");
+}
+
+}  // namespace sy
+
+extern "C" size_t sy_sort_scratch_bytes(int m, int n_experts) {
+  if (m <= sy::SORT_SINGLE_MAX || n_experts <= 0) return 0;
+  return (size_t)sy::sort_shape(m).blocks * n_experts * sizeof(int);
+}
+
+extern "C" int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n_experts, int dtype,
+                                 int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                                 void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(m >= 0 && top_k >= 1, "sort_by_expert: bad sizes (m=%d, k=%d)", m, top_k);
+  SY_REQUIRE(n_experts >= 1 && n_experts <= SORT_MAX_E, "sort_by_expert: at most %d experts (got %d)", SORT_MAX_E,
+             n_experts);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "sort_by_expert: dtype must be f16 or bf16");
+  SY_REQUIRE(counts && offsets, "sort_by_expert: null output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (m == 0) {
+    SY_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, s));
+    SY_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (n_experts + 1), s));
+    return SY_OK;
+  }
+  SY_REQUIRE(idx && w && token && wsorted && pos_of, "sort_by_expert: null pointer");
+  size_t need = sy_sort_scratch_bytes(m, n_experts);
+  SY_REQUIRE(need == 0 || (scratch && scratch_bytes >= need), "sort_by_expert: %zu bytes of scratch needed, %zu given",
+             need, scratch_bytes);
+  return dtype == SY_DTYPE_F16
+             ? launch_sort<__half>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch, s)
+             : launch_sort<__nv_bfloat16>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch,
+                                          s);
+}

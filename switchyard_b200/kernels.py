@@ -1,0 +1,255 @@
+"""The MoE layer's kernels behind the reference's `kernels.py` API.
+
+Same module-level names, argument order, defaults and return values as the reference
+(switchyard/kernels.py:12-93), so code written against it (its `ep.CudaOps`, its benches, the
+`moe=` hook of its `Model`) runs unchanged. Underneath, `ext()` is not a JIT-built torch
+extension but a ctypes binding of this package's C-ABI library of hand-written sm_100a
+kernels; this module allocates outputs with torch, checks shapes and dtypes, looks up the
+current stream and raises RuntimeError on any failure. There is no CPU path and no other
+backend: without the built library every call raises.
+
+Differences a caller can observe:
+  * fp16 and bf16 are both accepted (the reference is fp16 only);
+  * `grouped_gemm` ignores `tile_offsets` / `total_tiles`: tiles are scheduled on the device
+    from `offsets`, so the "gemm" mode never reads anything back to the host;
+  * there is no cuBLAS mode; "cublas" is accepted as an alias of "gemm";
+  * `experts(mode="auto")` chooses from the token count, not from a device-to-host read of
+    the largest expert's row count, so the layer never synchronises.
+"""
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_EXT = None
+
+
+def _dtype_code(t, what):
+    if t.dtype == torch.float16:
+        return _lib.SY_DTYPE_F16
+    if t.dtype == torch.bfloat16:
+        return _lib.SY_DTYPE_BF16
+    raise RuntimeError(f"{what}: fp16 or bf16 expected, got {t.dtype}")
+
+
+def _check(t, name):
+    if not (t.is_cuda and t.is_contiguous()):
+        raise RuntimeError(f"{name} must be a contiguous CUDA tensor")
+    return t
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+class _Device:
+    """Makes `dev` the current CUDA device for the call when it is not already."""
+
+    __slots__ = ("dev", "prev")
+
+    def __init__(self, dev):
+        self.dev = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.dev:
+            self.prev = cur
+            torch.cuda.set_device(self.dev)
+        return torch.cuda.current_stream(self.dev).cuda_stream
+
+    def __exit__(self, *a):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+class Ext:
+    """The eight operations of the reference's extension module
+    (switchyard/csrc/moe_kernels.cu:491-500), on torch tensors."""
+
+    def __init__(self):
+        self.lib = _lib.load()
+
+    def route(self, logits, k, norm):
+        _check(logits, "logits")
+        N, E = logits.shape
+        code = _dtype_code(logits, "route")
+        idx = torch.empty(N, k, dtype=torch.int32, device=logits.device)
+        w = torch.empty(N, k, dtype=logits.dtype, device=logits.device)
+        with _Device(logits.device) as stream:
+            _lib.check(self.lib.sy_route(_ptr(logits), N, E, int(k), int(bool(norm)), code, _ptr(idx), _ptr(w), stream),
+                       "route")
+        return [idx, w]
+
+    def sort_by_expert(self, idx, w, E):
+        _check(idx, "idx"), _check(w, "w")
+        if idx.dtype != torch.int32:
+            raise RuntimeError("sort_by_expert: idx must be int32")
+        M = idx.numel()
+        k = idx.shape[1] if idx.dim() == 2 else 1
+        code = _dtype_code(w, "sort_by_expert")
+        dev = idx.device
+        ints = torch.empty(2 * E + 1 + 2 * M, dtype=torch.int32, device=dev)
+        counts, offsets = ints[:E], ints[E:2 * E + 1]
+        token, pos_of = ints[2 * E + 1:2 * E + 1 + M], ints[2 * E + 1 + M:]
+        wsorted = torch.empty(M, dtype=w.dtype, device=dev)
+        need = self.lib.sy_sort_scratch_bytes(M, int(E))
+        scratch = torch.empty(need, dtype=torch.uint8, device=dev) if need else None
+        with _Device(dev) as stream:
+            _lib.check(self.lib.sy_sort_by_expert(_ptr(idx), _ptr(w), M, k, int(E), code, _ptr(counts), _ptr(offsets),
+                                                  _ptr(token), _ptr(wsorted), _ptr(pos_of), _ptr(scratch), need, stream),
+                       "sort_by_expert")
+        return [counts, offsets, token, wsorted, pos_of]
+
+    def _grouped(self, fn, name, A, a_rows, B, offsets, rows, swiglu, scale):
+        _check(A, "A"), _check(B, "B"), _check(offsets, "offsets")
+        code = _dtype_code(A, name)
+        if B.dtype != A.dtype:
+            raise RuntimeError(f"{name}: A and B must have the same dtype")
+        E, Nfull, K = B.shape
+        if A.shape[1] != K:
+            raise RuntimeError(f"{name}: K must match (A has {A.shape[1]}, B has {K})")
+        if offsets.dtype != torch.int32 or offsets.numel() != E + 1:
+            raise RuntimeError(f"{name}: offsets must be int32 [E+1]")
+        if a_rows is not None:
+            _check(a_rows, "a_rows")
+            if a_rows.dtype != torch.int32:
+                raise RuntimeError(f"{name}: a_rows must be int32")
+        if scale is not None:
+            _check(scale, "scale")
+        Nout = Nfull // 2 if swiglu else Nfull
+        C = torch.empty(rows, Nout, dtype=A.dtype, device=A.device)
+        if rows == 0:
+            return C
+        with _Device(A.device) as stream:
+            _lib.check(fn(_ptr(A), _ptr(a_rows), _ptr(B), _ptr(offsets), E, int(rows), Nout, K, int(bool(swiglu)),
+                          _ptr(scale), _ptr(C), code, stream), name)
+        return C
+
+    def grouped_gemm(self, A, a_rows, B, offsets, tile_offsets, total_tiles, rows, swiglu, scale):
+        return self._grouped(self.lib.sy_grouped_gemm, "grouped_gemm", A, a_rows, B, offsets, rows, swiglu, scale)
+
+    def grouped_gemv(self, A, a_rows, B, offsets, rows, swiglu, scale):
+        return self._grouped(self.lib.sy_grouped_gemv, "grouped_gemv", A, a_rows, B, offsets, rows, swiglu, scale)
+
+    def combine(self, y, pos_of, idx, n_tokens):
+        _check(y, "y"), _check(pos_of, "pos_of"), _check(idx, "idx")
+        code = _dtype_code(y, "combine")
+        H, k = y.shape[1], idx.shape[1]
+        out = torch.empty(n_tokens, H, dtype=y.dtype, device=y.device)
+        if n_tokens == 0:
+            return out
+        with _Device(y.device) as stream:
+            _lib.check(self.lib.sy_combine(_ptr(y), _ptr(pos_of), _ptr(idx), int(n_tokens), k, H, _ptr(out), code, stream),
+                       "combine")
+        return out
+
+    def gather_rows(self, src, index, dst):
+        _check(src, "src"), _check(index, "index"), _check(dst, "dst")
+        n, H = index.numel(), src.shape[1]
+        row_bytes = H * src.element_size()
+        if row_bytes % 16 or dst.shape[0] != n or dst.shape[1] != H or dst.dtype != src.dtype:
+            raise RuntimeError("gather_rows: shapes")
+        if n == 0:
+            return
+        with _Device(src.device) as stream:  # the kernel runs where the rows are read
+            _lib.check(self.lib.sy_gather_rows(_ptr(src), _ptr(index), n, row_bytes, _ptr(dst), stream), "gather_rows")
+
+    def copy_async(self, dst, src):
+        nbytes = src.numel() * src.element_size()
+        if not (dst.is_contiguous() and src.is_contiguous()) or dst.numel() * dst.element_size() != nbytes:
+            raise RuntimeError("copy_async: shapes")
+        if nbytes == 0:
+            return
+        with _Device(src.device) as stream:
+            _lib.check(self.lib.sy_copy_async(_ptr(dst), _ptr(src), nbytes, stream), "copy_async")
+
+    def enable_peer_access(self, device, peer):
+        ok = ctypes.c_int(0)
+        _lib.check(self.lib.sy_enable_peer_access(int(device), int(peer), ctypes.byref(ok)), "enable_peer_access")
+        return bool(ok.value)
+
+    def device_status(self, device=None):
+        """Waits for the current stream and returns (and clears) the device's kernel status
+        word: 0 unless a kernel gave up on a bounded wait. For tests and error paths."""
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        v = ctypes.c_int(0)
+        with _Device(dev) as stream:
+            _lib.check(self.lib.sy_device_status(stream, ctypes.byref(v)), "device_status")
+        return v.value
+
+
+def ext():
+    """The kernel library (loaded on first use). Raises RuntimeError if it was not built."""
+    global _EXT
+    if _EXT is None:
+        _EXT = Ext()
+    return _EXT
+
+
+def tile_offsets(counts, block=64):
+    """Cumulative row tiles per expert (switchyard/kernels.py:23-27). Kept for callers of the
+    reference API; this library's grouped_gemm does not use it."""
+    tiles = (counts + block - 1) // block
+    off = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
+    off[1:] = torch.cumsum(tiles, 0)
+    return off
+
+
+def route(h, router, top_k, norm_topk_prob):
+    """Router GEMM in h's dtype, then the routing kernel: (indices int32 [N,k], weights [N,k])
+    (switchyard/kernels.py:30-32)."""
+    return ext().route(F.linear(h, router).contiguous(), top_k, norm_topk_prob)
+
+
+# Rows per expert up to which the weight-streaming kernel is used by "auto"; beyond it the
+# tensor-core kernel. Measured on a B200 with OLMoE's shapes.
+GEMV_MAX_ROWS = 8
+GEMM_MAX_ROWS = 1 << 30  # no third mode on this hardware: the tensor-core kernel has no upper limit
+
+
+def pick(max_rows):
+    """Mode for a batch whose largest expert has `max_rows` rows (switchyard/kernels.py:41-45)."""
+    return "gemv" if max_rows <= GEMV_MAX_ROWS else "gemm"
+
+
+def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_counts=None):
+    """The experts over rows already sorted by expert: row i is x[a_rows[i]] (or x[i] when
+    a_rows is None); expert e owns rows offsets[e]:offsets[e+1]. Returns each row's expert
+    output scaled by its router weight, [rows, H] (switchyard/kernels.py:48-73). `counts` and
+    `host_counts` are accepted for compatibility; neither kernel needs them."""
+    E = ext()
+    if rows == 0:
+        return torch.empty(0, down.shape[1], dtype=x.dtype, device=x.device)
+    x = x.contiguous()
+    if mode == "gemv":
+        act = E.grouped_gemv(x, a_rows, gate_up, offsets, rows, True, None)
+        return E.grouped_gemv(act, None, down, offsets, rows, False, wsorted)
+    if mode in ("gemm", "cublas"):
+        act = E.grouped_gemm(x, a_rows, gate_up, offsets, None, 0, rows, True, None)
+        return E.grouped_gemm(act, None, down, offsets, None, 0, rows, False, wsorted)
+    raise RuntimeError(f"ffn: unknown mode {mode!r}")
+
+
+def experts(h, idx, w, gate_up, down, mode="auto"):
+    """The experts of one MoE layer on this GPU for routing (idx, w) computed already: sort by
+    expert, SwiGLU projection reading rows of h in place, down projection scaled by the router
+    weights, combine (switchyard/kernels.py:76-88). idx int32 [N,k] of local expert ids."""
+    E = ext()
+    N = h.shape[0]
+    idx = idx.contiguous()
+    counts, offsets, token, wsorted, pos_of = E.sort_by_expert(idx, w.contiguous(), gate_up.shape[0])
+    if mode == "auto":
+        mode = pick(N)  # an expert gets at most one row per token: N bounds the largest expert
+    y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode)
+    return E.combine(y, pos_of, idx, N)
+
+
+def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
+    """route + experts (switchyard/kernels.py:91-93)."""
+    idx, w = route(h, router, top_k, norm_topk_prob)
+    return experts(h, idx, w, gate_up, down, mode)
