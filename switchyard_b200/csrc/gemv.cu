@@ -34,6 +34,61 @@ constexpr int GV_MAX_E = 256;
 constexpr int GV_MAX_STAGES = 12;
 constexpr int GV_SMEM_BUDGET = 227 * 1024 - 2560;  // dynamic shared memory (the rest is static)
 
+// One warp, one output column of one stage, NR activation rows: float32 dot products over the
+// warp's 16-byte slices, xor-butterfly reduction, epilogue, store. NR is a compile-time
+// constant so that no instruction is spent on rows that are not there.
+template <typename T, bool SWIGLU, bool SCALE, int NR>
+__device__ __forceinline__ void gemv_column(const T* __restrict__ wrow, const T* __restrict__ urow,
+                                            const T* __restrict__ xs, int K, int lane, uint64_t* empty_bar,
+                                            const T* __restrict__ scale, T* __restrict__ C, int row0, int col,
+                                            int Nout) {
+  float acc[NR], accu[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) acc[r] = accu[r] = 0.f;
+#pragma unroll 2
+  for (int kk = lane * 8; kk < K; kk += 256) {
+    float wf[8], uf[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(wrow + kk), wf);
+    if (SWIGLU) unpack8<T>(*reinterpret_cast<const uint4*>(urow + kk), uf);
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      float xf[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)r * K + kk), xf);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        acc[r] = fmaf(xf[q], wf[q], acc[r]);
+        if (SWIGLU) accu[r] = fmaf(xf[q], uf[q], accu[r]);
+      }
+    }
+  }
+  // the stage is read: hand it back before the reduction
+  __syncwarp();
+  if (lane == 0) mbar_arrive(empty_bar);
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+      if (SWIGLU) accu[r] += __shfl_xor_sync(0xffffffffu, accu[r], o);
+    }
+  }
+  if (lane < NR) {
+    float v = 0.f, g = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+      if (r == lane) {
+        v = acc[r];
+        g = accu[r];
+      }
+    const int row = row0 + lane;
+    T o;
+    if (SWIGLU) o = epilogue_swiglu<T>(v, g);
+    else if (SCALE) o = epilogue_scale<T>(v, scale[row]);
+    else o = Elem<T>::from_f(v);
+    C[(size_t)row * Nout + col] = o;
+  }
+}
+
 template <typename T, bool SWIGLU, bool SCALE>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_stream_kernel(const T* __restrict__ A, const int* __restrict__ a_rows, const T* __restrict__ B,
@@ -148,54 +203,16 @@ gemv_stream_kernel(const T* __restrict__ A, const int* __restrict__ a_rows, cons
         const unsigned char* stage = ring + (size_t)s * stage_bytes;
         const T* wrow = reinterpret_cast<const T*>(stage + (size_t)warp * row_bytes);
         const T* urow = reinterpret_cast<const T*>(stage + (size_t)(GV_COLS + warp) * row_bytes);
-        float acc[GV_ROWS], accu[GV_ROWS];
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) acc[r] = accu[r] = 0.f;
-        for (int kk = lane * 8; kk < K; kk += 256) {
-          float wf[8], uf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(wrow + kk), wf);
-          if (SWIGLU) unpack8<T>(*reinterpret_cast<const uint4*>(urow + kk), uf);
-#pragma unroll
-          for (int r = 0; r < GV_ROWS; ++r) {
-            if (r < nr) {
-              float xf[8];
-              unpack8<T>(*reinterpret_cast<const uint4*>(xs + (size_t)r * K + kk), xf);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                acc[r] = fmaf(xf[q], wf[q], acc[r]);
-                if (SWIGLU) accu[r] = fmaf(xf[q], uf[q], accu[r]);
-              }
-            }
-          }
+        const int col = (uu - ue * groups) * GV_COLS + warp;
+#define SY_GEMV_CASE(NR)                                                                                         \
+  case NR:                                                                                                       \
+    gemv_column<T, SWIGLU, SCALE, NR>(wrow, urow, xs, K, lane, &empty_bar[s], scale, C, r0, col, Nout);         \
+    break;
+        switch (nr) {
+          SY_GEMV_CASE(1) SY_GEMV_CASE(2) SY_GEMV_CASE(3) SY_GEMV_CASE(4)
+          SY_GEMV_CASE(5) SY_GEMV_CASE(6) SY_GEMV_CASE(7) SY_GEMV_CASE(8)
         }
-        // the stage is read: hand it back before the reduction
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r) {
-          if (r < nr) {
-#pragma unroll
-            for (int o = 16; o; o >>= 1) {
-              acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
-              if (SWIGLU) accu[r] += __shfl_xor_sync(0xffffffffu, accu[r], o);
-            }
-          }
-        }
-        if (lane < nr) {
-          float v = 0.f, g = 0.f;
-#pragma unroll
-          for (int r = 0; r < GV_ROWS; ++r)
-            if (r == lane) {
-              v = acc[r];
-              g = accu[r];
-            }
-          const int row = r0 + lane, col = (uu - ue * groups) * GV_COLS + warp;
-          T o;
-          if (SWIGLU) o = epilogue_swiglu<T>(v, g);
-          else if (SCALE) o = epilogue_scale<T>(v, scale[row]);
-          else o = Elem<T>::from_f(v);
-          C[(size_t)row * Nout + col] = o;
-        }
+#undef SY_GEMV_CASE
       }
     }
     u = seg_end;
