@@ -315,7 +315,7 @@ def run_single_gpu(args):
                 "api": "switchyard_b200.kernels.moe_layer, eager, host buffers pinned"},
         "gpu_launches": args.steps * len(SWEEP) * 5,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "gemv_stream_kernel<half, SWIGLU>",
+                     "traffic": None, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, SWIGLU, streaming shape> (sy_grouped_gemv)",
                      "workload": "T=64 gate/up projection, one launch per layer in rotation",
                      "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
                      "vs_nominal_8TBps": achieved / 8000.0},

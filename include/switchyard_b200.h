@@ -65,15 +65,19 @@ int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n
                       int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
                       void* scratch, size_t scratch_bytes, void* stream);
 
-/* grouped_gemv — replaces `grouped_gemv` (moe_kernels.cu:385-415, kernel l.306-383).
+/* grouped_gemv — replaces `grouped_gemv` (moe_kernels.cu:385-415, kernel l.306-383): the decode
+ * path, for batches with few rows per expert, where the layer is bound by reading weights.
  * For every sorted row r of expert e (offsets[e] <= r < offsets[e+1]):
  *   C[r, :] = A[src(r), :] . B[e]^T,  src(r) = a_rows ? a_rows[r] : r
  * A 16-bit [*, k_dim]; B 16-bit [n_experts, n_full, k_dim] (nn.Linear layout per expert),
  * n_full = swiglu ? 2*n_out (gate rows first, then up rows) : n_out; C 16-bit [rows, n_out].
  * swiglu: C = silu(gate) * up with 16-bit rounding after each step; scale (16-bit [rows], may
- * be NULL, not with swiglu): C = round16(acc) * scale[r]. Accumulation is float32 in a fixed
- * order per row, so a row's bits do not depend on which other rows share its expert.
- * The decode path: a persistent weight stream, bulk-async copies into shared memory.
+ * be NULL, not with swiglu): C = round16(acc) * scale[r]. float32 accumulation in a fixed
+ * order per row: a row's bits do not depend on which other rows share its expert.
+ * A persistent weight stream: experts without rows are skipped, weight tiles (128 rows x 128 k,
+ * with swiglu 64 gate + 64 up rows) come in by TMA through a four-stage shared-memory ring,
+ * the dot products run on tcgen05 with the token rows as the N operand (N = rows rounded up
+ * to 16, at most 64 per tile), accumulators in tensor memory. Any row count is accepted.
  * Requirements: k_dim % 8 == 0, n_out % 8 == 0, 16-byte aligned A, B; n_experts <= 256. */
 int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                     int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
@@ -81,10 +85,10 @@ int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const i
 
 /* grouped_gemm — replaces `grouped_gemm` (moe_kernels.cu:264-298, kernel l.159-261) and the
  * host-side `tile_offsets` / `total_tiles` arguments, which this implementation does not need:
- * work is scheduled on the device from `offsets`. Same contraction and epilogues as
- * sy_grouped_gemv, computed on the tcgen05 tensor cores with accumulators in tensor memory,
- * expert weights fed by TMA and activation rows gathered from A in-kernel.
- * Requirements: k_dim % 64 == 0, n_out % 64 == 0, 16-byte aligned A, 128-byte aligned B. */
+ * tiles are scheduled on the device from `offsets`. Same contract as sy_grouped_gemv; the same
+ * kernel in its compute-bound shape: 128 token rows per tile against two 128-row weight tiles
+ * (gate and up of the same columns with swiglu) in two tensor-memory accumulators, rows
+ * gathered from A in-kernel, epilogues fused. */
 int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                     int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                     int dtype, void* stream);

@@ -1,37 +1,38 @@
-// grouped_gemm: every expert's slice of the sorted batch on the tcgen05 tensor cores.
+// grouped_gemm and grouped_gemv: every expert's slice of the sorted batch on the tcgen05 tensor
+// cores. One kernel in two shapes (see Shape below): "gemm" for compute-bound batches, "gemv"
+// for decode, where the layer is a stream over expert weights.
 //
 // Orientation. The weight tile is the MMA's M operand and the token rows are its N operand
 // ("C^T = W . X^T"): an instruction multiplies 128 weight rows by up to 128 token rows over 16
-// k. That keeps M = 128 full no matter how few rows an expert has, so the same kernel is a
-// weight stream for a handful of rows and a compute-bound GEMM for thousands; N is rounded up
-// to a multiple of 16 per tile.
+// k. That keeps M = 128 full no matter how few rows an expert has, so the same code is a
+// weight stream for a handful of rows and a GEMM for thousands; N is rounded up to a multiple
+// of 16 per tile. (A CUDA-core weight stream was built first and measured on a B200: float32
+// FMA keeps up with HBM3e only below about four rows per expert, 1.2 TB/s at 64 tokens, so the
+// decode path streams through the tensor cores too.)
 //
-// One tile = (expert, 128 token rows, a pair of 128-row weight tiles that share the token
-// operand). With SwiGLU fused the pair is gate rows [c, c+128) and up rows [c, c+128) of the
-// same output columns, so the epilogue has both halves in tensor memory; otherwise it is 256
-// consecutive output columns. The grid is persistent (one block per SM); tiles are numbered on
-// the device from `offsets` (expert-major, an expert's row tiles adjacent so that its weights
-// are read from HBM once and then hit L2) and dealt round-robin, so nothing about the batch
-// is read back to the host.
+// One tile = (expert, a block of token rows, a block of output columns). The grid is
+// persistent (one block per SM); tiles are numbered on the device from `offsets` (expert-major,
+// an expert's row tiles adjacent so that its weights are read from HBM once and then hit L2)
+// and dealt round-robin, so nothing about the batch is read back to the host.
 //
 // A block is fourteen warps with fixed roles, connected by mbarriers:
-//   warp 0      TMA producer: the two weight tiles of each 64-wide k block, 128-byte swizzle;
+//   warp 0      TMA producer: the weight tiles of each k block, 128-byte swizzle;
 //   warps 2-9   gather producers: the tile's token rows, picked from the UNSORTED activations
-//               through a_rows, loaded 16 bytes per thread (prefetched one k block ahead in
-//               registers) and stored to shared memory in the same swizzled layout;
-//   warp 1      MMA issuer: one thread, tcgen05.mma into one of two accumulator pairs in
+//               through a_rows, 16-byte cp.async copies straight into the same swizzled layout,
+//               several k blocks in flight per thread;
+//   warp 1      MMA issuer: one thread, tcgen05.mma into one of two accumulator buffers in
 //               tensor memory; tcgen05.commit releases the stage / publishes the accumulators;
 //   warps 10-13 epilogue: tcgen05.ld of the accumulators (a thread owns one output column and
 //               walks the token rows), SwiGLU or router-weight scaling with the 16-bit
 //               rounding points, stores. It overlaps the next tile's main loop.
-// Four 48 KB stages; tensor memory: 2 buffers x 2 accumulators x 128 columns = all 512.
 //
 // An output element is a sum over k in instruction order that does not depend on which other
 // rows share the tile or on the tile's N, so a row's bits are the same on one GPU and inside
-// an expert-parallel segment.
+// an expert-parallel segment (within one shape; the two shapes are separate modes).
 //
 // Replaces switchyard/csrc/moe_kernels.cu:159-298 (64x64x32 WMMA tiles, one block per tile,
-// tile list built by torch on the host).
+// tile list built by torch on the host) and l.306-415 (CUDA-core GEMV, one block per expert and
+// 32 columns, blocks launched for empty experts too).
 #include <cuda.h>
 
 #include <atomic>
@@ -42,62 +43,102 @@
 
 namespace sy {
 
-constexpr int GM_BK = 64;                          // k per stage: 128-byte rows
-constexpr int GM_BM = 128;                         // weight rows per MMA tile
-constexpr int GM_BN = 128;                         // token rows per tile
-constexpr int GM_STAGES = 4;
-constexpr int GM_TILE_BYTES = GM_BM * GM_BK * 2;   // 16 KB
-constexpr int GM_STAGE_BYTES = 3 * GM_TILE_BYTES;  // W0, W1, X
+constexpr int GM_ATOM_K = 64;                      // k per swizzle atom: 128-byte rows
+constexpr int GM_BM = 128;                         // weight rows per accumulator (UMMA M)
 constexpr int GM_GATHER_WARPS = 8;
 constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_GATHER_WARPS + GM_EPI_WARPS) * 32;
-constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_MAX_E = 256;
-constexpr int GM_SMEM = GM_STAGES * GM_STAGE_BYTES + 1024;  // + room to align to 1024
+constexpr int GM_RING_BYTES = 192 * 1024;          // shared-memory ring of stages
+constexpr int GM_SMEM = GM_RING_BYTES + 1024;      // + room to align the ring to 1024
 constexpr uint64_t GM_WAIT_NS = 1000000000ull;
+
+// Two shapes of the same kernel.
+//   PAIR   (mode "gemm"): 128 token rows per tile, two 128-row weight tiles sharing them (two
+//          accumulators), 48 KB stages x 4: the compute-bound shape.
+//   !PAIR  (mode "gemv"): 64 token rows per tile, one 128-row weight tile (with SwiGLU: 64 gate
+//          rows + 64 up rows of the same columns) over 128 k per stage (two swizzle atoms), so a
+//          stage carries the same 32 KB of weights and the same eight MMAs as a PAIR stage, but
+//          tiles are half as large and twice as many: less imbalance when every tile is one
+//          pass over an expert's weights.
+template <bool PAIR> struct Shape {
+  static constexpr int BN = PAIR ? 128 : 64;               // token rows per tile (UMMA N max)
+  static constexpr int BOX_ROWS = PAIR ? 128 : 64;         // weight rows per TMA box (two boxes per atom)
+  static constexpr int KATOMS = PAIR ? 1 : 2;              // 64-wide k atoms per stage
+  static constexpr int BK = KATOMS * GM_ATOM_K;            // k per stage
+  static constexpr int W_ATOM_BYTES = 2 * BOX_ROWS * 128;  // weight bytes of one atom (both boxes)
+  static constexpr int X_ATOM_BYTES = BN * 128;
+  static constexpr int W_BYTES = KATOMS * W_ATOM_BYTES;    // weight bytes per stage (32 KB either way)
+  static constexpr int X_BYTES = KATOMS * X_ATOM_BYTES;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int STAGES = GM_RING_BYTES / STAGE_BYTES;
+  static constexpr int ACCS = PAIR ? 2 : 1;                // accumulators per tile
+  static constexpr int BUF_COLS = ACCS * BN;               // tensor-memory columns per buffer
+  static constexpr int TMEM_COLS = 2 * BUF_COLS;           // two buffers: 512 or 128
+};
 
 struct Tile {
   int e, cb, row0, nvalid;
 };
 
+// Optional per-role cycle accounting (compiled in only with -DSY_PROFILE; used when tuning).
+#ifdef SY_PROFILE
+__device__ long long g_prof[256][16];
+#define SY_PROF_DECL(n) long long n = 0
+#define SY_PROF_BEGIN(t) long long t = clock64()
+#define SY_PROF_ADD(acc, t) acc += clock64() - t
+#define SY_PROF_STORE(slot, v) g_prof[blockIdx.x][slot] = (v)
+#else
+#define SY_PROF_DECL(n)
+#define SY_PROF_BEGIN(t)
+#define SY_PROF_ADD(acc, t)
+#define SY_PROF_STORE(slot, v)
+#endif
+
 // Tile t of the device-side numbering; `cursor` walks the experts monotonically.
+template <int BN>
 __device__ __forceinline__ Tile locate_tile(int t, int& cursor, const int* tile_start, const int* off) {
   while (tile_start[cursor + 1] <= t) ++cursor;
   const int e = cursor, local = t - tile_start[e];
-  const int n = off[e + 1] - off[e], row_tiles = (n + GM_BN - 1) / GM_BN;
+  const int n = off[e + 1] - off[e], row_tiles = (n + BN - 1) / BN;
   Tile tile;
   tile.e = e;
   tile.cb = local / row_tiles;
-  tile.row0 = off[e] + (local % row_tiles) * GM_BN;
-  tile.nvalid = min(GM_BN, off[e + 1] - tile.row0);
+  tile.row0 = off[e] + (local % row_tiles) * BN;
+  tile.nvalid = min(BN, off[e + 1] - tile.row0);
   return tile;
 }
 
-template <typename T, bool SWIGLU, bool SCALE>
+template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict__ A,
                  const int* __restrict__ a_rows, const int* __restrict__ offsets, int E, int Nout, int K,
                  const T* __restrict__ scale, T* __restrict__ C, int* status) {
+  using S = Shape<PAIR>;
+  constexpr int BN = S::BN, STAGES = S::STAGES, STAGE_BYTES = S::STAGE_BYTES;
+  // output columns per tile
+  constexpr int COLS = SWIGLU ? (PAIR ? GM_BM : GM_BM / 2) : (PAIR ? 2 * GM_BM : GM_BM);
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[GM_STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[GM_STAGES];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_off[GM_MAX_E + 1];
   __shared__ int s_tile_start[GM_MAX_E + 2];
+  __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (!PAIR SwiGLU)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* stages =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
 
-  const int col_blocks = SWIGLU ? (Nout + GM_BM - 1) / GM_BM : (Nout + 2 * GM_BM - 1) / (2 * GM_BM);
+  const int col_blocks = (Nout + COLS - 1) / COLS;
   const int Nfull = SWIGLU ? 2 * Nout : Nout;
-  const int k_blocks = (K + GM_BK - 1) / GM_BK;
+  const int k_blocks = (K + S::BK - 1) / S::BK;
 
   for (int i = threadIdx.x; i <= E; i += GM_THREADS) s_off[i] = offsets[i];
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GM_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1 + GM_GATHER_WARPS);
       mbar_init(&empty_bar[s], 1);
     }
@@ -114,7 +155,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     for (int base = 0; base < E; base += 32) {
       int e = base + lane;
       int n = e < E ? s_off[e + 1] - s_off[e] : 0;
-      int tiles = ((n + GM_BN - 1) / GM_BN) * col_blocks, inc = tiles;
+      int tiles = ((n + BN - 1) / BN) * col_blocks, inc = tiles;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         int y = __shfl_up_sync(0xffffffffu, inc, o);
@@ -129,7 +170,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     }
   }
   if (warp == 1) {
-    tmem_alloc(&s_tmem, GM_TMEM_COLS);
+    tmem_alloc(&s_tmem, S::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -143,165 +184,247 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     if (lane == 0) {
       int it = 0, cursor = 0;
       bool alive = true;
+      SY_PROF_DECL(w_empty);
+      SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-        const Tile tile = locate_tile(t, cursor, s_tile_start, s_off);
-        const int y0 = tile.e * Nfull + (SWIGLU ? tile.cb * GM_BM : tile.cb * 2 * GM_BM);
-        const int y1 = SWIGLU ? tile.e * Nfull + Nout + tile.cb * GM_BM : y0 + GM_BM;
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
+        const int y0 = tile.e * Nfull + tile.cb * COLS;
+        const int y1 = SWIGLU ? y0 + Nout : y0 + S::BOX_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % GM_STAGES, use = it / GM_STAGES;
+          const int s = it % STAGES, use = it / STAGES;
+          SY_PROF_BEGIN(t_w);
           if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS)) {
             *status = DS_TIMEOUT_EMPTY;
             alive = false;
             break;
           }
-          unsigned char* st = stages + (size_t)s * GM_STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], 2 * GM_TILE_BYTES);
-          tma_load_2d(st, &w_map, kb * GM_BK, y0, &full_bar[s]);
-          tma_load_2d(st + GM_TILE_BYTES, &w_map, kb * GM_BK, y1, &full_bar[s]);
+          SY_PROF_ADD(w_empty, t_w);
+          unsigned char* st = stages + (size_t)s * STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], S::W_BYTES);
+#pragma unroll
+          for (int a = 0; a < S::KATOMS; ++a) {
+            const int kx = kb * S::BK + a * GM_ATOM_K;
+            tma_load_2d(st + a * S::W_ATOM_BYTES, &w_map, kx, y0, &full_bar[s]);
+            tma_load_2d(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &w_map, kx, y1, &full_bar[s]);
+          }
         }
       }
+      SY_PROF_STORE(0, w_empty);
+      SY_PROF_STORE(1, clock64() - t_role);
       if (!alive)  // let the copies already issued land before the block can exit
-        for (int j = it > GM_STAGES ? it - GM_STAGES : 0; j < it; ++j)
-          mbar_wait(&full_bar[j % GM_STAGES], (j / GM_STAGES) & 1, 10000000ull);
+        for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j)
+          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      const uint32_t ring_lo = umma_desc_lo(smem_u32(stages));
       int it = 0, cursor = 0, tile_no = 0;
       bool alive = true;
+      SY_PROF_DECL(w_full);
+      SY_PROF_DECL(w_acc);
+      SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_no) {
-        const Tile tile = locate_tile(t, cursor, s_tile_start, s_off);
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
         const int buf = tile_no & 1, use_t = tile_no >> 1;
         if (use_t > 0) {
+          SY_PROF_BEGIN(t_w);
           if (!mbar_wait(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS)) {
             *status = DS_TIMEOUT_TMEM;
             alive = false;
             break;
           }
+          SY_PROF_ADD(w_acc, t_w);
           tc_fence_after_sync();
         }
         const int n_mma = max(16, (tile.nvalid + 15) & ~15);
         const uint32_t idesc = umma_idesc(fmt, GM_BM, n_mma);
-        const uint32_t d0 = tmem + buf * 2 * GM_BN, d1 = d0 + GM_BN;
+        const uint32_t d0 = tmem + buf * S::BUF_COLS, d1 = d0 + BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % GM_STAGES;
-          if (!mbar_wait(&full_bar[s], (it / GM_STAGES) & 1, GM_WAIT_NS)) {
+          const int s = it % STAGES;
+          SY_PROF_BEGIN(t_w);
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, GM_WAIT_NS)) {
             *status = DS_TIMEOUT_FULL;
             alive = false;
             break;
           }
+          SY_PROF_ADD(w_full, t_w);
           tc_fence_after_sync();
-          const uint32_t base = smem_u32(stages + (size_t)s * GM_STAGE_BYTES);
+          const uint32_t lo = ring_lo + s * (STAGE_BYTES >> 4);  // descriptor low word of the stage's first tile
 #pragma unroll
-          for (int ks = 0; ks < GM_BK / 16; ++ks) {
-            const uint64_t a0 = umma_desc_k_sw128(base + ks * 32);
-            const uint64_t a1 = umma_desc_k_sw128(base + GM_TILE_BYTES + ks * 32);
-            const uint64_t b = umma_desc_k_sw128(base + 2 * GM_TILE_BYTES + ks * 32);
+          for (int ks = 0; ks < S::BK / 16; ++ks) {
             const uint32_t accumulate = (kb | ks) != 0;
-            umma_f16(d0, a0, b, idesc, accumulate);
-            umma_f16(d1, a1, b, idesc, accumulate);
+            const int atom = ks >> 2, within = (ks & 3) * 2;  // 32 bytes per 16 k inside the 128-byte atom
+            const uint32_t a_lo = lo + atom * (S::W_ATOM_BYTES >> 4) + within;
+            const uint32_t b_lo = lo + (S::W_BYTES >> 4) + atom * (S::X_ATOM_BYTES >> 4) + within;
+            umma_f16_lohi(d0, a_lo, b_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
+            if (PAIR) umma_f16_lohi(d1, a_lo + (S::BOX_ROWS * 128 >> 4), b_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
           }
           umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
         if (alive) umma_commit(&acc_full[buf]);
       }
+      SY_PROF_STORE(2, w_full);
+      SY_PROF_STORE(3, w_acc);
+      SY_PROF_STORE(4, clock64() - t_role);
+      SY_PROF_STORE(5, (long long)it);
     }
   } else if (warp < 2 + GM_GATHER_WARPS) {
     // ---------------------------------------------------------------- gather producers
+    // 16-byte asynchronous copies straight into the swizzled stage, DEPTH k blocks in flight
+    // per thread (commit groups), so that the L2 round trip of a gathered row is overlapped
+    // with the stages before it. A stage is published (proxy fence, then one arrive per warp)
+    // once the group that filled it has landed; filling runs ahead across tile boundaries.
+    constexpr int CHUNKS = S::BK / 8;                 // 16-byte chunks per token row per stage
+    constexpr int ROWS_PER_PASS = GM_GATHER_WARPS * 32 / CHUNKS;
+    constexpr int GI = BN / ROWS_PER_PASS;
+    constexpr int DEPTH = STAGES - 1;
     const int g = threadIdx.x - 64;
-    const int c = g & 7, rsub = g >> 3;  // 16-byte chunk of the 128-byte row; row within a group of 32
-    int it = 0, cursor = 0;
+    const int c = g % CHUNKS, rsub = g / CHUNKS;      // chunk of the row; row within a pass
+    const int xoff = (c >> 3) * S::X_ATOM_BYTES;      // the atom the chunk belongs to
+    const int cc = c & 7;
+    int issued = 0, published = 0, cursor = 0;
     bool alive = true;
+    SY_PROF_DECL(w_empty);
+    SY_PROF_DECL(w_group);
+    SY_PROF_DECL(w_rows);
+    SY_PROF_BEGIN(t_role);
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-      const Tile tile = locate_tile(t, cursor, s_tile_start, s_off);
-      const T* src[4];
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
+      const T* src[GI];
+      SY_PROF_BEGIN(t_r);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = rsub + 32 * i;
+      for (int i = 0; i < GI; ++i) {
+        const int r = rsub + ROWS_PER_PASS * i;
         src[i] = nullptr;
         if (r < tile.nvalid) {
           const int row = a_rows ? a_rows[tile.row0 + r] : tile.row0 + r;
           src[i] = A + (size_t)row * K + c * 8;
         }
       }
-      uint4 cur[4], nxt[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        cur[i] = make_uint4(0, 0, 0, 0);
-        if (src[i] && c * 8 < K) cur[i] = __ldg(reinterpret_cast<const uint4*>(src[i]));
-      }
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-        const int k_next = (kb + 1) * GM_BK + c * 8;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          nxt[i] = make_uint4(0, 0, 0, 0);
-          if (src[i] && kb + 1 < k_blocks && k_next < K)
-            nxt[i] = __ldg(reinterpret_cast<const uint4*>(src[i] + (size_t)(kb + 1) * GM_BK));
-        }
-        const int s = it % GM_STAGES, use = it / GM_STAGES;
+      SY_PROF_ADD(w_rows, t_r);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int s = issued % STAGES, use = issued / STAGES;
+        SY_PROF_BEGIN(t_w);
         if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS)) {
           *status = DS_TIMEOUT_EMPTY;
           alive = false;
           break;
         }
-        unsigned char* x = stages + (size_t)s * GM_STAGE_BYTES + 2 * GM_TILE_BYTES;
+        SY_PROF_ADD(w_empty, t_w);
+        unsigned char* x = stages + (size_t)s * STAGE_BYTES + S::W_BYTES + xoff;
+        const uint32_t bytes = kb * S::BK + c * 8 < K ? 16u : 0u;  // beyond K: zero fill
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = rsub + 32 * i;
-          if (r < tile.nvalid) *reinterpret_cast<uint4*>(x + r * 128 + ((c ^ (r & 7)) << 4)) = cur[i];
+        for (int i = 0; i < GI; ++i) {
+          const int r = rsub + ROWS_PER_PASS * i;
+          if (src[i]) cp_async_16(x + r * 128 + ((cc ^ (r & 7)) << 4), bytes ? src[i] + (size_t)kb * S::BK : src[i], bytes);
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_bar[s]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
+        cp_async_commit();
+        ++issued;
+        if (issued - published > DEPTH) {
+          SY_PROF_BEGIN(t_g);
+          cp_async_wait<DEPTH>();
+          SY_PROF_ADD(w_group, t_g);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[published % STAGES]);
+          ++published;
+        }
       }
     }
+    if (threadIdx.x == 64) {
+      SY_PROF_STORE(6, w_empty);
+      SY_PROF_STORE(7, w_group);
+      SY_PROF_STORE(8, w_rows);
+      SY_PROF_STORE(9, clock64() - t_role);
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    __syncwarp();
+    for (; published < issued; ++published)
+      if (lane == 0) mbar_arrive(&full_bar[published % STAGES]);
   } else {
     // ---------------------------------------------------------------- epilogue
+    // A warp that gives up on a wait keeps walking the tiles (the exchange barrier below must
+    // still see all four warps) but skips every wait, load and store.
     const int q = warp & 3;  // the quarter of tensor memory's lanes this warp may read
-    int cursor = 0, tile_no = 0;
+    int cursor = 0, tile_no = 0, chunk_no = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_no) {
-      const Tile tile = locate_tile(t, cursor, s_tile_start, s_off);
+    SY_PROF_DECL(w_accf);
+    SY_PROF_BEGIN(t_role);
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
       const int buf = tile_no & 1, use_t = tile_no >> 1;
-      if (!mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
+      SY_PROF_BEGIN(t_w);
+      if (alive && !mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
         *status = DS_TIMEOUT_MMA;
         alive = false;
-        break;
       }
+      SY_PROF_ADD(w_accf, t_w);
       tc_fence_after_sync();
-      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * 2 * GM_BN;
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * S::BUF_COLS;
       const int wrow = q * 32 + lane;
-      const int col0 = SWIGLU ? tile.cb * GM_BM + wrow : tile.cb * 2 * GM_BM + wrow;
-      const int col1 = col0 + GM_BM;  // second accumulator's column (not used with SwiGLU)
-      for (int n0 = 0; n0 < tile.nvalid; n0 += 8) {
-        uint32_t v0[8], v1[8];
-        tmem_ld_x8(taddr + n0, v0);
-        tmem_ld_x8(taddr + GM_BN + n0, v1);
-        tmem_ld_wait();
+      if (PAIR || !SWIGLU) {
+        const int col0 = tile.cb * COLS + wrow;
+        const int col1 = col0 + GM_BM;  // the second accumulator's column (PAIR without SwiGLU)
+        for (int n0 = 0; n0 < tile.nvalid && alive; n0 += 8) {
+          uint32_t v0[8], v1[8];
+          tmem_ld_x8(taddr + n0, v0);
+          if (PAIR) tmem_ld_x8(taddr + BN + n0, v1);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int row = tile.row0 + n0 + j;
-          if (n0 + j < tile.nvalid) {
-            const float f0 = __uint_as_float(v0[j]), f1 = __uint_as_float(v1[j]);
-            if (SWIGLU) {
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
-            } else if (SCALE) {
-              const T sc = scale[row];
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
-              if (col1 < Nout) C[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
-            } else {
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
-              if (col1 < Nout) C[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
+          for (int j = 0; j < 8; ++j) {
+            const int row = tile.row0 + n0 + j;
+            if (n0 + j < tile.nvalid) {
+              const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
+              if (SWIGLU) {
+                if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
+              } else if (SCALE) {
+                const T sc = scale[row];
+                if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
+                if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
+              } else {
+                if (col0 < Nout) C[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
+                if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
+              }
+            }
+          }
+        }
+      } else {
+        // one accumulator: lanes 0-63 hold the gate rows, lanes 64-127 the up rows of the same
+        // 64 output columns. Warps 2,3 pass their values to warps 0,1 through shared memory.
+        const int j64 = wrow & 63;
+        const int col = tile.cb * COLS + j64;
+        for (int n0 = 0; n0 < tile.nvalid; n0 += 8, ++chunk_no) {
+          uint32_t v[8];
+          if (alive) {
+            tmem_ld_x8(taddr + n0, v);
+            tmem_ld_wait();
+          }
+          float* slot = s_xch[chunk_no & 1][j64];
+          if (q >= 2 && alive) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
+          }
+          named_barrier_sync(2, GM_EPI_WARPS * 32);
+          if (q < 2 && alive) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int row = tile.row0 + n0 + j;
+              if (n0 + j < tile.nvalid && col < Nout)
+                C[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
             }
           }
         }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0 && alive) mbar_arrive(&acc_empty[buf]);
+    }
+    if (threadIdx.x == 320) {
+      SY_PROF_STORE(10, w_accf);
+      SY_PROF_STORE(11, clock64() - t_role);
     }
   }
 
@@ -310,7 +433,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, GM_TMEM_COLS);
+    tmem_dealloc(tmem, S::TMEM_COLS);
   }
 }
 
@@ -335,14 +458,14 @@ static int encode_fn(EncodeTiledFn* out) {
   return SY_OK;
 }
 
-// Tensor map over the stacked expert weights as a [rows, K] matrix; box = 128 rows x 64 k.
-static int weight_map(CUtensorMap* map, const void* B, uint64_t rows, uint64_t K, int dtype) {
+// Tensor map over the stacked expert weights as a [rows, K] matrix; box = box_rows x 64 k.
+static int weight_map(CUtensorMap* map, const void* B, uint64_t rows, uint64_t K, int dtype, int box_rows) {
   EncodeTiledFn encode;
   int rc = encode_fn(&encode);
   if (rc != SY_OK) return rc;
   cuuint64_t dims[2] = {K, rows};
   cuuint64_t strides[1] = {K * 2};
-  cuuint32_t box[2] = {GM_BK, GM_BM};
+  cuuint32_t box[2] = {GM_ATOM_K, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
   CUresult r = encode(map, dtype == SY_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                       2, const_cast<void*>(B), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -351,15 +474,18 @@ static int weight_map(CUtensorMap* map, const void* B, uint64_t rows, uint64_t K
   return SY_OK;
 }
 
-template <typename T, bool SWIGLU, bool SCALE>
-static int launch_gemm(const CUtensorMap& map, const void* A, const int32_t* a_rows, const int32_t* offsets, int E,
-                       int Nout, int K, const void* scale, void* C, cudaStream_t stream) {
+template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
+static int launch_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets, int E, int Nout,
+                       int K, const void* scale, void* C, int dtype, cudaStream_t stream) {
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != SY_OK) return rc;
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
-  auto kern = gemm_umma_kernel<T, SWIGLU, SCALE>;
+  CUtensorMap map;
+  rc = weight_map(&map, B, (uint64_t)E * (SWIGLU ? 2 : 1) * Nout, (uint64_t)K, dtype, Shape<PAIR>::BOX_ROWS);
+  if (rc != SY_OK) return rc;
+  auto kern = gemm_umma_kernel<T, SWIGLU, SCALE, PAIR>;
   static std::atomic<int> configured[MAX_DEVICES];
   int dev = 0;
   SY_CUDA(cudaGetDevice(&dev));
@@ -369,38 +495,56 @@ static int launch_gemm(const CUtensorMap& map, const void* A, const int32_t* a_r
   }
   kern<<<sms, GM_THREADS, GM_SMEM, stream>>>(map, static_cast<const T*>(A), a_rows, offsets, E, Nout, K,
                                              static_cast<const T*>(scale), static_cast<T*>(C), status);
-  return check_cuda(cudaGetLastError(), "grouped_gemm launch");
+  return check_cuda(cudaGetLastError(), "grouped tcgen05 launch");
 }
 
-template <typename T>
-static int dispatch_gemm(const CUtensorMap& map, const void* A, const int32_t* a_rows, const int32_t* offsets, int E,
-                         int Nout, int K, int swiglu, const void* scale, void* C, cudaStream_t stream) {
-  if (swiglu) return launch_gemm<T, true, false>(map, A, a_rows, offsets, E, Nout, K, nullptr, C, stream);
-  if (scale) return launch_gemm<T, false, true>(map, A, a_rows, offsets, E, Nout, K, scale, C, stream);
-  return launch_gemm<T, false, false>(map, A, a_rows, offsets, E, Nout, K, nullptr, C, stream);
+template <typename T, bool PAIR>
+static int dispatch_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets, int E, int Nout,
+                         int K, int swiglu, const void* scale, void* C, int dtype, cudaStream_t stream) {
+  if (swiglu) return launch_gemm<T, true, false, PAIR>(A, a_rows, B, offsets, E, Nout, K, nullptr, C, dtype, stream);
+  if (scale) return launch_gemm<T, false, true, PAIR>(A, a_rows, B, offsets, E, Nout, K, scale, C, dtype, stream);
+  return launch_gemm<T, false, false, PAIR>(A, a_rows, B, offsets, E, Nout, K, nullptr, C, dtype, stream);
+}
+
+// Shared argument checks and dtype dispatch of the two tensor-core entry points.
+int grouped_umma(bool pair, const char* name, const void* A, const int32_t* a_rows, const void* B,
+                 const int32_t* offsets, int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale,
+                 void* C, int dtype, void* stream) {
+  SY_REQUIRE(rows >= 0 && n_experts >= 1 && n_experts <= GM_MAX_E, "%s: 1..%d experts (got %d)", name, GM_MAX_E,
+             n_experts);
+  SY_REQUIRE(k_dim > 0 && k_dim % 8 == 0, "%s: k_dim must be a multiple of 8 (got %d)", name, k_dim);
+  SY_REQUIRE(n_out > 0 && n_out % 8 == 0, "%s: n_out must be a multiple of 8 (got %d)", name, n_out);
+  SY_REQUIRE(!(swiglu && scale), "%s: swiglu and scale are separate epilogues", name);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "%s: dtype must be f16 or bf16", name);
+  if (rows == 0) return SY_OK;
+  SY_REQUIRE(A && B && offsets && C, "%s: null pointer", name);
+  SY_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0), "%s: A and B must be 16-byte aligned", name);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == SY_DTYPE_F16)
+    return pair ? dispatch_gemm<__half, true>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s)
+                : dispatch_gemm<__half, false>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s);
+  return pair ? dispatch_gemm<__nv_bfloat16, true>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s)
+              : dispatch_gemm<__nv_bfloat16, false>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s);
 }
 
 }  // namespace sy
 
+#ifdef SY_PROFILE
+extern "C" int sy_prof_read(long long* out, int blocks) {
+  return sy::check_cuda(cudaMemcpyFromSymbol(out, sy::g_prof, sizeof(long long) * 16 * blocks), "prof read");
+}
+#endif
+
 extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                                int dtype, void* stream) {
-  using namespace sy;
-  SY_REQUIRE(rows >= 0 && n_experts >= 1 && n_experts <= GM_MAX_E, "grouped_gemm: 1..%d experts (got %d)", GM_MAX_E,
-             n_experts);
-  SY_REQUIRE(k_dim > 0 && k_dim % 8 == 0, "grouped_gemm: k_dim must be a multiple of 8 (got %d)", k_dim);
-  SY_REQUIRE(n_out > 0 && n_out % 8 == 0, "grouped_gemm: n_out must be a multiple of 8 (got %d)", n_out);
-  SY_REQUIRE(!(swiglu && scale), "grouped_gemm: swiglu and scale are separate epilogues");
-  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "grouped_gemm: dtype must be f16 or bf16");
-  if (rows == 0) return SY_OK;
-  SY_REQUIRE(A && B && offsets && C, "grouped_gemm: null pointer");
-  SY_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0), "grouped_gemm: A and B must be 16-byte aligned");
-  const uint64_t n_full = (uint64_t)(swiglu ? 2 : 1) * n_out;
-  CUtensorMap map;
-  int rc = weight_map(&map, B, (uint64_t)n_experts * n_full, (uint64_t)k_dim, dtype);
-  if (rc != SY_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return dtype == SY_DTYPE_F16
-             ? dispatch_gemm<__half>(map, A, a_rows, offsets, n_experts, n_out, k_dim, swiglu, scale, C, s)
-             : dispatch_gemm<__nv_bfloat16>(map, A, a_rows, offsets, n_experts, n_out, k_dim, swiglu, scale, C, s);
+  return sy::grouped_umma(true, "grouped_gemm", A, a_rows, B, offsets, n_experts, rows, n_out, k_dim, swiglu, scale, C,
+                          dtype, stream);
+}
+
+extern "C" int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
+                               int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
+                               int dtype, void* stream) {
+  return sy::grouped_umma(false, "grouped_gemv", A, a_rows, B, offsets, n_experts, rows, n_out, k_dim, swiglu, scale, C,
+                          dtype, stream);
 }

@@ -42,6 +42,8 @@ def test_version_and_argument_errors(lib):
     assert rc == -1 and b"top_k" in lib.sy_last_error()
     rc = lib.sy_grouped_gemv(None, None, None, None, 64, 8, 100, 64, 0, None, None, 0, None)
     assert rc == -1 and b"multiple of 8" in lib.sy_last_error()
+    rc = lib.sy_grouped_gemm(None, None, None, None, 64, 8, 64, 60, 0, None, None, 0, None)
+    assert rc == -1 and b"multiple of 8" in lib.sy_last_error()
     assert lib.sy_sort_scratch_bytes(512, 64) == 0
     assert lib.sy_sort_scratch_bytes(65536, 64) > 0
 
