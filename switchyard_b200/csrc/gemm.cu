@@ -96,24 +96,29 @@ __device__ long long g_prof[256][16];
 #endif
 
 // Tile t of the device-side numbering; `cursor` walks the experts monotonically.
+// A group is a set of consecutive rows [begin, end) that goes through one expert's weights:
+// an expert's slice of the sorted batch, or, in an expert-parallel mailbox, one sender's rows
+// for one local expert.
 template <int BN>
-__device__ __forceinline__ Tile locate_tile(int t, int& cursor, const int* tile_start, const int* off) {
+__device__ __forceinline__ Tile locate_tile(int t, int& cursor, const int* tile_start, const int* begin,
+                                            const int* end) {
   while (tile_start[cursor + 1] <= t) ++cursor;
   const int e = cursor, local = t - tile_start[e];
-  const int n = off[e + 1] - off[e], row_tiles = (n + BN - 1) / BN;
+  const int n = end[e] - begin[e], row_tiles = (n + BN - 1) / BN;
   Tile tile;
   tile.e = e;
   tile.cb = local / row_tiles;
-  tile.row0 = off[e] + (local % row_tiles) * BN;
-  tile.nvalid = min(BN, off[e + 1] - tile.row0);
+  tile.row0 = begin[e] + (local % row_tiles) * BN;
+  tile.nvalid = min(BN, end[e] - tile.row0);
   return tile;
 }
 
 template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict__ A,
-                 const int* __restrict__ a_rows, const int* __restrict__ offsets, int E, int Nout, int K,
-                 const T* __restrict__ scale, T* __restrict__ C, int* status) {
+                 const int* __restrict__ a_rows, const int* __restrict__ begins, const int* __restrict__ ends, int E,
+                 int weight_sets, int Nout, int K, const T* __restrict__ scale, T* __restrict__ C,
+                 const unsigned long long* __restrict__ c_table, int* status) {
   using S = Shape<PAIR>;
   constexpr int BN = S::BN, STAGES = S::STAGES, STAGE_BYTES = S::STAGE_BYTES;
   // output columns per tile
@@ -124,7 +129,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
-  __shared__ int s_off[GM_MAX_E + 1];
+  __shared__ int s_begin[GM_MAX_E];
+  __shared__ int s_end[GM_MAX_E];
   __shared__ int s_tile_start[GM_MAX_E + 2];
   __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (!PAIR SwiGLU)
 
@@ -136,7 +142,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   const int Nfull = SWIGLU ? 2 * Nout : Nout;
   const int k_blocks = (K + S::BK - 1) / S::BK;
 
-  for (int i = threadIdx.x; i <= E; i += GM_THREADS) s_off[i] = offsets[i];
+  for (int i = threadIdx.x; i < E; i += GM_THREADS) {
+    const int b = begins[i], e = ends[i];
+    s_begin[i] = b;
+    s_end[i] = e > b ? e : b;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1 + GM_GATHER_WARPS);
@@ -154,7 +164,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     int carry = 0;
     for (int base = 0; base < E; base += 32) {
       int e = base + lane;
-      int n = e < E ? s_off[e + 1] - s_off[e] : 0;
+      int n = e < E ? s_end[e] - s_begin[e] : 0;
       int tiles = ((n + BN - 1) / BN) * col_blocks, inc = tiles;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -187,8 +197,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       SY_PROF_DECL(w_empty);
       SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
-        const int y0 = tile.e * Nfull + tile.cb * COLS;
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
+        const int y0 = (tile.e % weight_sets) * Nfull + tile.cb * COLS;
         const int y1 = SWIGLU ? y0 + Nout : y0 + S::BOX_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES, use = it / STAGES;
@@ -226,7 +236,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       SY_PROF_DECL(w_acc);
       SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_no) {
-        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
         const int buf = tile_no & 1, use_t = tile_no >> 1;
         if (use_t > 0) {
           SY_PROF_BEGIN(t_w);
@@ -291,7 +301,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     SY_PROF_DECL(w_rows);
     SY_PROF_BEGIN(t_role);
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
       const T* src[GI];
       SY_PROF_BEGIN(t_r);
 #pragma unroll
@@ -354,7 +364,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     SY_PROF_DECL(w_accf);
     SY_PROF_BEGIN(t_role);
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
-      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_off);
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
       const int buf = tile_no & 1, use_t = tile_no >> 1;
       SY_PROF_BEGIN(t_w);
       if (alive && !mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
@@ -365,6 +375,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       tc_fence_after_sync();
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * S::BUF_COLS;
       const int wrow = q * 32 + lane;
+      // where this group's rows go: C, or (expert-parallel return) wherever c_table says the
+      // group's first row lands, possibly in a peer GPU's memory
+      T* __restrict__ Cg = c_table ? reinterpret_cast<T*>(c_table[tile.e]) - (size_t)s_begin[tile.e] * Nout : C;
       if (PAIR || !SWIGLU) {
         const int col0 = tile.cb * COLS + wrow;
         const int col1 = col0 + GM_BM;  // the second accumulator's column (PAIR without SwiGLU)
@@ -379,14 +392,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
             if (n0 + j < tile.nvalid) {
               const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
               if (SWIGLU) {
-                if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
+                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
               } else if (SCALE) {
                 const T sc = scale[row];
-                if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
-                if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
+                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
+                if (PAIR && col1 < Nout) Cg[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
               } else {
-                if (col0 < Nout) C[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
-                if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
+                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
+                if (PAIR && col1 < Nout) Cg[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
               }
             }
           }
@@ -413,7 +426,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
             for (int j = 0; j < 8; ++j) {
               const int row = tile.row0 + n0 + j;
               if (n0 + j < tile.nvalid && col < Nout)
-                C[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
+                Cg[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
             }
           }
         }
@@ -474,16 +487,32 @@ static int weight_map(CUtensorMap* map, const void* B, uint64_t rows, uint64_t K
   return SY_OK;
 }
 
+struct GroupedArgs {
+  const void* A;
+  const int32_t* a_rows;
+  const void* B;
+  const int32_t* begins;   // [groups] first row of each group
+  const int32_t* ends;     // [groups] one past its last row
+  int groups;              // number of groups (an expert's slice; or sender x local expert)
+  int weight_sets;         // group g uses weights B[g % weight_sets]
+  int n_out, k_dim;
+  const void* scale;
+  void* C;
+  const unsigned long long* c_table;  // optional per-group output row pointers
+  int dtype;
+  cudaStream_t stream;
+};
+
 template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
-static int launch_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets, int E, int Nout,
-                       int K, const void* scale, void* C, int dtype, cudaStream_t stream) {
+static int launch_gemm(const GroupedArgs& a) {
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != SY_OK) return rc;
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
   CUtensorMap map;
-  rc = weight_map(&map, B, (uint64_t)E * (SWIGLU ? 2 : 1) * Nout, (uint64_t)K, dtype, Shape<PAIR>::BOX_ROWS);
+  rc = weight_map(&map, a.B, (uint64_t)a.weight_sets * (SWIGLU ? 2 : 1) * a.n_out, (uint64_t)a.k_dim, a.dtype,
+                  Shape<PAIR>::BOX_ROWS);
   if (rc != SY_OK) return rc;
   auto kern = gemm_umma_kernel<T, SWIGLU, SCALE, PAIR>;
   static std::atomic<int> configured[MAX_DEVICES];
@@ -493,38 +522,32 @@ static int launch_gemm(const void* A, const int32_t* a_rows, const void* B, cons
     SY_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
     configured[dev].store(1, std::memory_order_release);
   }
-  kern<<<sms, GM_THREADS, GM_SMEM, stream>>>(map, static_cast<const T*>(A), a_rows, offsets, E, Nout, K,
-                                             static_cast<const T*>(scale), static_cast<T*>(C), status);
+  kern<<<sms, GM_THREADS, GM_SMEM, a.stream>>>(map, static_cast<const T*>(a.A), a.a_rows, a.begins, a.ends, a.groups,
+                                               a.weight_sets, a.n_out, a.k_dim, static_cast<const T*>(a.scale),
+                                               static_cast<T*>(a.C), a.c_table, status);
   return check_cuda(cudaGetLastError(), "grouped tcgen05 launch");
 }
 
 template <typename T, bool PAIR>
-static int dispatch_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets, int E, int Nout,
-                         int K, int swiglu, const void* scale, void* C, int dtype, cudaStream_t stream) {
-  if (swiglu) return launch_gemm<T, true, false, PAIR>(A, a_rows, B, offsets, E, Nout, K, nullptr, C, dtype, stream);
-  if (scale) return launch_gemm<T, false, true, PAIR>(A, a_rows, B, offsets, E, Nout, K, scale, C, dtype, stream);
-  return launch_gemm<T, false, false, PAIR>(A, a_rows, B, offsets, E, Nout, K, nullptr, C, dtype, stream);
+static int dispatch_gemm(const GroupedArgs& a, int swiglu) {
+  if (swiglu) return launch_gemm<T, true, false, PAIR>(a);
+  if (a.scale) return launch_gemm<T, false, true, PAIR>(a);
+  return launch_gemm<T, false, false, PAIR>(a);
 }
 
-// Shared argument checks and dtype dispatch of the two tensor-core entry points.
-int grouped_umma(bool pair, const char* name, const void* A, const int32_t* a_rows, const void* B,
-                 const int32_t* offsets, int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale,
-                 void* C, int dtype, void* stream) {
-  SY_REQUIRE(rows >= 0 && n_experts >= 1 && n_experts <= GM_MAX_E, "%s: 1..%d experts (got %d)", name, GM_MAX_E,
-             n_experts);
-  SY_REQUIRE(k_dim > 0 && k_dim % 8 == 0, "%s: k_dim must be a multiple of 8 (got %d)", name, k_dim);
-  SY_REQUIRE(n_out > 0 && n_out % 8 == 0, "%s: n_out must be a multiple of 8 (got %d)", name, n_out);
-  SY_REQUIRE(!(swiglu && scale), "%s: swiglu and scale are separate epilogues", name);
-  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "%s: dtype must be f16 or bf16", name);
+// Shared argument checks and dtype dispatch of the tensor-core entry points.
+int grouped_umma(bool pair, const char* name, const GroupedArgs& a, int rows, int swiglu) {
+  SY_REQUIRE(rows >= 0 && a.groups >= 1 && a.groups <= GM_MAX_E, "%s: 1..%d groups (got %d)", name, GM_MAX_E, a.groups);
+  SY_REQUIRE(a.weight_sets >= 1 && a.weight_sets <= a.groups, "%s: bad number of weight sets %d", name, a.weight_sets);
+  SY_REQUIRE(a.k_dim > 0 && a.k_dim % 8 == 0, "%s: k_dim must be a multiple of 8 (got %d)", name, a.k_dim);
+  SY_REQUIRE(a.n_out > 0 && a.n_out % 8 == 0, "%s: n_out must be a multiple of 8 (got %d)", name, a.n_out);
+  SY_REQUIRE(!(swiglu && a.scale), "%s: swiglu and scale are separate epilogues", name);
+  SY_REQUIRE(a.dtype == SY_DTYPE_F16 || a.dtype == SY_DTYPE_BF16, "%s: dtype must be f16 or bf16", name);
   if (rows == 0) return SY_OK;
-  SY_REQUIRE(A && B && offsets && C, "%s: null pointer", name);
-  SY_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0), "%s: A and B must be 16-byte aligned", name);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == SY_DTYPE_F16)
-    return pair ? dispatch_gemm<__half, true>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s)
-                : dispatch_gemm<__half, false>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s);
-  return pair ? dispatch_gemm<__nv_bfloat16, true>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s)
-              : dispatch_gemm<__nv_bfloat16, false>(A, a_rows, B, offsets, n_experts, n_out, k_dim, swiglu, scale, C, dtype, s);
+  SY_REQUIRE(a.A && a.B && a.begins && a.ends && (a.C || a.c_table), "%s: null pointer", name);
+  SY_REQUIRE(((uintptr_t)a.A % 16 == 0) && ((uintptr_t)a.B % 16 == 0), "%s: A and B must be 16-byte aligned", name);
+  if (a.dtype == SY_DTYPE_F16) return pair ? dispatch_gemm<__half, true>(a, swiglu) : dispatch_gemm<__half, false>(a, swiglu);
+  return pair ? dispatch_gemm<__nv_bfloat16, true>(a, swiglu) : dispatch_gemm<__nv_bfloat16, false>(a, swiglu);
 }
 
 }  // namespace sy
@@ -538,13 +561,24 @@ extern "C" int sy_prof_read(long long* out, int blocks) {
 extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                                int dtype, void* stream) {
-  return sy::grouped_umma(true, "grouped_gemm", A, a_rows, B, offsets, n_experts, rows, n_out, k_dim, swiglu, scale, C,
-                          dtype, stream);
+  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, n_experts, n_out, k_dim,
+                    scale, C, nullptr, dtype, static_cast<cudaStream_t>(stream)};
+  return sy::grouped_umma(true, "grouped_gemm", a, rows, swiglu);
 }
 
 extern "C" int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                                int dtype, void* stream) {
-  return sy::grouped_umma(false, "grouped_gemv", A, a_rows, B, offsets, n_experts, rows, n_out, k_dim, swiglu, scale, C,
-                          dtype, stream);
+  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, n_experts, n_out, k_dim,
+                    scale, C, nullptr, dtype, static_cast<cudaStream_t>(stream)};
+  return sy::grouped_umma(false, "grouped_gemv", a, rows, swiglu);
+}
+
+extern "C" int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, const int32_t* ends,
+                                   int n_groups, int weight_sets, int rows_bound, int n_out, int k_dim, int swiglu,
+                                   const void* scale, void* C, const uint64_t* c_table, int dtype, int compute_shape,
+                                   void* stream) {
+  sy::GroupedArgs a{A, nullptr, B, begins, ends, n_groups, weight_sets, n_out, k_dim, scale, C,
+                    reinterpret_cast<const unsigned long long*>(c_table), dtype, static_cast<cudaStream_t>(stream)};
+  return sy::grouped_umma(compute_shape != 0, "grouped_segments", a, rows_bound, swiglu);
 }
