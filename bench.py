@@ -326,13 +326,40 @@ def run_single_gpu(args):
     print(json.dumps(line), flush=True)
 
 
+def run_case(spec):
+    """--case MODE:T[:bf16][:zipf]: three passes of one layer shape and nothing else. This is the
+    small, self-ending program that ncu captures are taken from (two resident weight sets)."""
+    from switchyard_b200 import kernels, synthetic
+    parts = spec.split(":")
+    mode, T = parts[0], int(parts[1])
+    dtype = torch.bfloat16 if "bf16" in parts[2:] else torch.float16
+    dev = torch.device("cuda:0")
+    layers = [synthetic.layer_weights(dev, dtype, seed=100 + l) for l in range(2)]
+    h = synthetic.hidden_states(T, dev, dtype, seed=T)
+    bias = synthetic.zipf_bias().to(dev).to(dtype) if "zipf" in parts[2:] else None
+    for i in range(3):
+        router, gu, dn = layers[i % 2]
+        if bias is None:
+            out = kernels.moe_layer(h, router, gu, dn, TOPK, False, mode)
+        else:
+            logits = (torch.nn.functional.linear(h, router) + bias).contiguous()
+            idx, w = kernels.ext().route(logits, TOPK, False)
+            out = kernels.experts(h, idx, w, gu, dn, mode)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": spec, "checksum": float(out.float().abs().sum()),
+                      "device_status": kernels.ext().device_status(dev)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] - run one small layer shape (for profiling)")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args.case)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
