@@ -115,6 +115,56 @@ int sy_copy_async(void* dst, const void* src, size_t bytes, void* stream);
  * Already-enabled is not an error. */
 int sy_enable_peer_access(int device, int peer, int* enabled_out);
 
+/* ---- expert parallelism with one process per GPU ------------------------------------------
+ * The entry points below have no single counterpart in the reference: together they replace
+ * the body of ExpertParallel.phase_send / phase_compute / phase_combine (switchyard/ep.py:174-272)
+ * — per destination a gather_rows + three copy_async + an event, per received segment an ffn +
+ * a copy back + an event — with five launches per layer that never involve the host.
+ * See csrc/ep.cu for the protocol. All pointer tables are HOST arrays of device pointers. */
+
+/* grouped_segments — sy_grouped_gemv (compute_shape = 0) or sy_grouped_gemm (1) over explicit
+ * row groups: group g is rows [begins[g], ends[g]) of A (no gather) and uses the weights
+ * B[g / groups_per_expert]. begins/ends are device arrays of n_groups ints. If c_table is not
+ * NULL, row begins[g] + i of group g is stored at ((T*)c_table[g]) + i*n_out instead of in C (the
+ * destination may be a peer GPU's memory). rows_bound: any upper bound of the rows (0 = no-op). */
+int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, const int32_t* ends, int n_groups,
+                        int groups_per_expert, int rows_bound, int n_out, int k_dim, int swiglu, const void* scale,
+                        void* C, const uint64_t* c_table, int dtype, int compute_shape, void* stream);
+
+/* ep_dispatch — sends every sorted row to the rank owning its expert: row i (expert in
+ * [d*experts_per_rank, (d+1)*experts_per_rank)) is copied from h[token[i]] to row
+ * i - offsets[d*experts_per_rank] of x_dst[d], its router weight to w_dst[d]; meta_dst[d] gets
+ * experts_per_rank+1 rebased offsets, the segment's first row and its row count; finally
+ * *flag_dst[d] = epoch (release, system scope) for every d. done_counter: one zero-initialised
+ * int of this rank's memory. Rows past `capacity` of a mailbox are dropped and reported through
+ * the status word. m == 0 still publishes (empty) mailboxes. */
+int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
+                   int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
+                   void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* done_counter,
+                   int epoch, void* stream);
+
+/* ep_wait_build — waits (bounded, 2 s) until arrive_flags[s] >= epoch for every sender, then
+ * builds the row groups of this rank's mailbox (group e*n_ranks + s = sender s's rows of local
+ * expert e; sender s's rows start at s*capacity) and c_table (where each group's results go:
+ * y_dst[s] + (first row of the segment in the sender's sort + rebased offset) * out_row_bytes). */
+int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
+                     int capacity, void* const* y_dst, int out_row_bytes, int epoch, int32_t* begins,
+                     int32_t* ends, uint64_t* c_table, void* stream);
+
+/* ep_signal — *flag_dst[s] = epoch (release, system scope) for every s, after everything
+ * enqueued before it on `stream` (the results written into the senders' memory) is done. */
+int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, int epoch, void* stream);
+
+/* ep_wait — waits (bounded, 2 s) until flags[i] >= epoch for i < n (n <= 32). */
+int sy_ep_wait(const int32_t* flags, int n, int epoch, void* stream);
+
+/* ipc_export / ipc_open / ipc_close — map one rank's window into another process (CUDA IPC).
+ * export: 64-byte handle of the allocation containing ptr and ptr's offset in it.
+ * open: the same address in this process (peer access enabled lazily). Set-up time only. */
+int sy_ipc_export(void* ptr, unsigned char* handle64, uint64_t* offset_out);
+int sy_ipc_open(const unsigned char* handle64, uint64_t offset, void** ptr_out);
+int sy_ipc_close(void* ptr, uint64_t offset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,174 @@
+"""`bench.py --gpus N` for N > 1: the same decode sweep as at N = 1, expert-parallel.
+
+One process per GPU (launched by torch.distributed.run), NCCL process group for set-up and for
+the max-over-ranks of the timings only. Every rank holds E/N experts of each resident weight
+set and T tokens of its own (T = 1, 8, 32, 64: weak scaling in tokens); a step is one
+expert-parallel layer at each T through `DistributedExpertParallel.layer` (dispatch and return
+by kernels writing into peer memory, no collective on the data path).
+
+  value  aggregate expert-weight GB/s: over all ranks, experts that received at least one row
+         (from any rank) x 3*H*I*2 bytes, divided by the slowest rank's device time;
+  e2e    the same with each rank's hidden states copied from pinned host memory and its output
+         copied back every pass."""
+
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+SWEEP = (1, 8, 32, 64)
+H, I, E, TOPK = 2048, 1024, 64, 8
+EXPERT_BYTES = 3 * H * I * 2
+LAYERS = 8
+METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
+
+
+def rank_weights(device, dtype, seed, lo, hi):
+    """Experts [lo, hi) of the weight set `seed` (same values as synthetic.layer_weights gives
+    for the whole set: the generator is advanced past the experts this rank does not hold)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    router = (torch.randn(E, H, device=device, generator=g) * 0.02).to(dtype)
+    gate_up = torch.empty(hi - lo, 2 * I, H, device=device, dtype=dtype)
+    down = torch.empty(hi - lo, H, I, device=device, dtype=dtype)
+    for e in range(hi):
+        a = torch.randn(2 * I, H, device=device, generator=g)
+        b = torch.randn(H, I, device=device, generator=g)
+        if e >= lo:
+            gate_up[e - lo] = (a * 0.02).to(dtype)
+            down[e - lo] = (b * 0.02).to(dtype)
+    return router, gate_up, down
+
+
+def run(args):
+    from . import kernels, synthetic
+    from .ep_dist import DistributedExpertParallel
+    import bench  # the repo-root script: clock sampler and peaks
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    dtype, mode = torch.float16, "gemv"
+    per = E // world
+    layers = [rank_weights(dev, dtype, 100 + l, rank * per, (rank + 1) * per) for l in range(LAYERS)]
+    hs = {T: synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T) for T in SWEEP}
+    ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=max(SWEEP), dtype=dtype, mode=mode, device=dev)
+
+    # experts used per (T, layer) over ALL ranks' tokens: fixed by the seeds; for the byte count
+    used = {}
+    for T in SWEEP:
+        for l, (router, _, _) in enumerate(layers):
+            idx, _ = kernels.route(hs[T], router, TOPK, False)
+            seen = torch.zeros(E, dtype=torch.int32, device=dev)
+            seen[idx.flatten().long()] = 1
+            dist.all_reduce(seen, op=dist.ReduceOp.MAX)
+            used[(T, l)] = int(seen.sum())
+    stream = torch.cuda.Stream(dev)
+    pass_no = [0]
+
+    def step(timed, evs):
+        for T in SWEEP:
+            l = pass_no[0] % LAYERS
+            pass_no[0] += 1
+            router, gu, dn = layers[l]
+            if timed:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+            ep.layer(hs[T], router, gu, dn)
+            if timed:
+                b.record(stream)
+                evs.append((T, l, a, b))
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step(False, None)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = bench.ClockSampler(dev.index).__enter__() if rank == 0 else None
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        evs = []
+        t0.record(stream)
+        for _ in range(args.steps):
+            step(True, evs)
+        t1.record(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    times = torch.tensor([t0.elapsed_time(t1)] + [sum(a.elapsed_time(b) for (T2, _, a, b) in evs if T2 == T) for T in SWEEP],
+                         dtype=torch.float64, device=dev)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms = float(times[0])
+    per_T_ms = {T: float(times[1 + i]) for i, T in enumerate(SWEEP)}
+    per_T_bytes = {T: sum(used[(T2, l)] for (T2, l, _, _) in evs if T2 == T) * EXPERT_BYTES for T in SWEEP}
+    total_bytes = sum(per_T_bytes.values())
+
+    # end to end with host buffers
+    host_in = {T: hs[T].cpu().pin_memory() for T in SWEEP}
+    host_out = {T: torch.empty(T, H, dtype=dtype).pin_memory() for T in SWEEP}
+    dev_in = {T: torch.empty_like(hs[T]) for T in SWEEP}
+
+    def e2e_step():
+        nbytes = 0
+        for T in SWEEP:
+            l = pass_no[0] % LAYERS
+            pass_no[0] += 1
+            router, gu, dn = layers[l]
+            dev_in[T].copy_(host_in[T], non_blocking=True)
+            out = ep.layer(dev_in[T], router, gu, dn)
+            host_out[T].copy_(out, non_blocking=True)
+            nbytes += used[(T, l)] * EXPERT_BYTES
+        torch.cuda.current_stream().synchronize()
+        return nbytes
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            e2e_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        e2e_bytes = sum(e2e_step() for _ in range(args.steps))
+        e1.record(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+    e2e_t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    status = torch.tensor([kernels.ext().device_status(dev)], device=dev)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    assert int(status) == 0, "a kernel gave up on a bounded wait"
+    ep.close()
+
+    if rank == 0:
+        peak, peak_src = bench.peaks()
+        io_bytes = sum(T * H * 2 for T in SWEEP) * world
+        value = total_bytes / (total_ms / 1e3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "configs[1] decode sweep T=1,8,32,64 tokens PER GPU, fp16, expert-parallel: "
+                                   f"{per} experts per GPU, P2P dispatch and return; a step = one layer at each T",
+                       "tokens_per_gpu": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK,
+                       "mode": mode, "parallelism": f"ep{world} (attention data-parallel)",
+                       "l2": f"passes rotate over {LAYERS} resident weight sets",
+                       "timing": "CUDA events on each rank's stream, eager launches, max over ranks"},
+            "sweep": [{"tokens_per_gpu": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
+                       "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
+                       "tokens_per_s": T * world * args.steps / (per_T_ms[T] / 1e3)} for T in SWEEP],
+            "clocks": clocks,
+            "e2e": {"value": e2e_bytes / (float(e2e_t) / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
+                    "d2h_bytes_per_step": io_bytes, "ms_per_step": float(e2e_t) / args.steps,
+                    "api": "switchyard_b200.ep_dist.DistributedExpertParallel.layer, host buffers pinned"},
+            "gpu_launches": args.steps * len(SWEEP) * 9 * world,
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "whole expert-parallel layer, per GPU (the weight-stream kernel is profiled at N=1)"},
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libswitchyard_b200.so")
-SOURCES = ["runtime.cu", "route.cu", "sort.cu", "combine.cu", "transport.cu", "gemm.cu"]
+SOURCES = ["runtime.cu", "route.cu", "sort.cu", "combine.cu", "transport.cu", "gemm.cu", "ep.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr"]
 

@@ -147,7 +147,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-// 2-D tiled TMA load global -> shared (no multicast), completion on an mbarrier.
+// 2-D tiled TMA load global -> shared of this CTA only, completion on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(void* dst_smem, const void* tensor_map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(

@@ -1,0 +1,268 @@
+// Expert-parallel transport for one process per GPU.
+//
+// Every rank owns a "window" of device memory that its peers map (CUDA IPC, or peer access in
+// one process): a mailbox per sender (rows, router weights, per-expert offsets) and the buffer
+// `y` that its own combine reads. One layer, per rank, all on the rank's stream, no host read:
+//
+//   dispatch    one launch: every sorted row goes to the rank that owns its expert, written
+//               straight into that rank's mailbox over NVLink (its own rows too, locally);
+//               rebased offsets, the segment's first row and its row count go with it; when the
+//               last block is done, a release-store of the layer's epoch into every receiver's
+//               arrival flag publishes the mailbox;
+//   wait+build  one block waits (bounded) for all senders' arrival flags, then turns the
+//               mailboxes' offsets into row groups (expert-major, one group per sender and local
+//               expert) and into the table of where each group's results must land: in the
+//               sender's `y`, at the rows the sender's own sort gave them;
+//   experts     the grouped tcgen05 kernel twice over those groups (csrc/gemm.cu); the second
+//               launch's epilogue stores each result row through the table, i.e. directly into
+//               the sender's memory: the return trip is fused into the down projection;
+//   signal      release-store of the epoch into every sender's return flag;
+//   wait        before the combine, one block waits for every owner's return flag.
+//
+// Flags only ever grow (the epoch is the layer counter), so nothing is reset between layers.
+// A mailbox is overwritten by layer n+1's dispatch only after its sender has passed layer n's
+// return wait, which the receiver signals after it has finished reading the mailbox.
+//
+// Every wait is bounded; on expiry the kernel records DS_TIMEOUT_FLAG in the status word and
+// lets the stream continue (the layer's output is then garbage and the host raises when it
+// next reads the status). Kernels that wait for another rank's flag must run on different GPUs
+// than the kernels that set it.
+//
+// Replaces the per-pair gather + three copies + event of switchyard/ep.py:193-223, the
+// per-segment ffn + copy back + event of l.239-262, and the event waits of l.264-272.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace sy {
+
+constexpr int EP_MAX_RANKS = 16;
+constexpr int EP_THREADS = 256;
+constexpr uint64_t EP_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until *flag >= epoch; false after EP_WAIT_NS.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (ld_acquire_sys(flag) >= epoch) return true;
+    if ((spin & 63u) == 0) {
+      if (global_timer_ns() - start > EP_WAIT_NS) return false;
+      __nanosleep(200);
+    }
+  }
+}
+
+struct DispatchTargets {
+  unsigned char* x[EP_MAX_RANKS];   // receiver d's mailbox rows for this sender
+  unsigned char* w[EP_MAX_RANKS];   // ... router weights
+  int* meta[EP_MAX_RANKS];          // ... [per+1 rebased offsets | first row | row count]
+  int* flag[EP_MAX_RANKS];          // ... arrival flag of this sender
+};
+
+__global__ void __launch_bounds__(EP_THREADS)
+ep_dispatch_kernel(const uint4* __restrict__ h, const int* __restrict__ token, const unsigned short* __restrict__ wsorted,
+                   const int* __restrict__ offsets, int M, int per, int R, int vec_per_row, int cap,
+                   DispatchTargets tg, int* done_counter, int epoch, int* status) {
+  __shared__ int s_seg[EP_MAX_RANKS + 1];
+  __shared__ int s_last;
+  if (threadIdx.x <= R) s_seg[threadIdx.x] = offsets[threadIdx.x * per];
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    const int meta_ints = per + 3;
+    for (int t = threadIdx.x; t < R * meta_ints; t += EP_THREADS) {
+      const int d = t / meta_ints, j = t - d * meta_ints;
+      int v;
+      if (j <= per) v = offsets[d * per + j] - s_seg[d];
+      else if (j == per + 1) v = s_seg[d];
+      else v = min(s_seg[d + 1] - s_seg[d], cap);
+      tg.meta[d][j] = v;
+    }
+  }
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    int d = 0;
+    while (d + 1 < R && s_seg[d + 1] <= row) ++d;
+    const int r = row - s_seg[d];
+    if (r >= cap) {  // cannot happen when the caller respects max_tokens; never write past a mailbox
+      if (threadIdx.x == 0) *status = DS_BAD_INDEX;
+      continue;
+    }
+    const uint4* src = h + (size_t)token[row] * vec_per_row;
+    uint4* dst = reinterpret_cast<uint4*>(tg.x[d]) + (size_t)r * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += EP_THREADS) dst[i] = __ldg(src + i);
+    if (threadIdx.x == 0) reinterpret_cast<unsigned short*>(tg.w[d])[r] = wsorted[row];
+  }
+  // last block out publishes the mailboxes
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(done_counter, 1) == (int)gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *done_counter = 0;
+    __threadfence_system();
+    if (threadIdx.x < R) st_release_sys(tg.flag[threadIdx.x], epoch);
+  }
+}
+
+struct ReturnTargets {
+  unsigned char* y[EP_MAX_RANKS];   // sender s's result buffer (its window's y)
+  int* flag[EP_MAX_RANKS];          // sender s's return flag for this rank
+};
+
+// Groups are expert-major: group g = e * R + s holds sender s's rows for local expert e.
+__global__ void __launch_bounds__(EP_THREADS)
+ep_wait_build_kernel(const int* arrive_flags, const int* meta, int per, int R, int cap,
+                     ReturnTargets rt, int out_row_bytes, int epoch, int* __restrict__ begins, int* __restrict__ ends,
+                     unsigned long long* __restrict__ c_table, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < R && !wait_flag(arrive_flags + threadIdx.x, epoch)) {
+    *status = DS_TIMEOUT_FLAG;
+    s_ok = 0;
+  }
+  __syncthreads();
+  const int meta_ints = per + 3;
+  for (int g = threadIdx.x; g < R * per; g += EP_THREADS) {
+    const int e = g / R, s = g - e * R;
+    const volatile int* m = meta + s * meta_ints;  // written by another GPU: no cached read
+    const int lo = s_ok ? m[e] : 0, hi = s_ok ? min(m[e + 1], cap) : 0;
+    begins[g] = s * cap + lo;
+    ends[g] = s * cap + (hi > lo ? hi : lo);
+    c_table[g] = reinterpret_cast<unsigned long long>(rt.y[s]) + (unsigned long long)(m[per + 1] + lo) * out_row_bytes;
+  }
+}
+
+__global__ void ep_signal_kernel(ReturnTargets rt, int R, int epoch) {
+  __threadfence_system();
+  if (threadIdx.x < R) st_release_sys(rt.flag[threadIdx.x], epoch);
+}
+
+__global__ void ep_wait_kernel(const int* __restrict__ flags, int n, int epoch, int* status) {
+  if (threadIdx.x < n && !wait_flag(flags + threadIdx.x, epoch)) *status = DS_TIMEOUT_FLAG;
+}
+
+}  // namespace sy
+
+extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
+                              int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
+                              void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst,
+                              int32_t* done_counter, int epoch, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS, "ep_dispatch: 1..%d ranks (got %d)", EP_MAX_RANKS, n_ranks);
+  SY_REQUIRE(m >= 0 && experts_per_rank >= 1 && capacity >= 1, "ep_dispatch: bad sizes");
+  SY_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "ep_dispatch: row size must be a multiple of 16 bytes");
+  SY_REQUIRE(offsets && x_dst && w_dst && meta_dst && flag_dst && done_counter, "ep_dispatch: null pointer");
+  SY_REQUIRE(m == 0 || (h && token && wsorted), "ep_dispatch: null pointer");
+  DispatchTargets tg;
+  for (int d = 0; d < n_ranks; ++d) {
+    tg.x[d] = static_cast<unsigned char*>(x_dst[d]);
+    tg.w[d] = static_cast<unsigned char*>(w_dst[d]);
+    tg.meta[d] = meta_dst[d];
+    tg.flag[d] = flag_dst[d];
+    SY_REQUIRE(tg.x[d] && tg.w[d] && tg.meta[d] && tg.flag[d] && (uintptr_t)tg.x[d] % 16 == 0,
+               "ep_dispatch: bad target for rank %d", d);
+  }
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != SY_OK) return rc;
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  int blocks = m < 1 ? 1 : (m < sms * 4 ? m : sms * 4);
+  ep_dispatch_kernel<<<blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(h), token, static_cast<const unsigned short*>(wsorted), offsets, m, experts_per_rank,
+      n_ranks, row_bytes / 16, capacity, tg, done_counter, epoch, status);
+  return check_cuda(cudaGetLastError(), "ep_dispatch launch");
+}
+
+extern "C" int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
+                                int capacity, void* const* y_dst, int out_row_bytes, int epoch, int32_t* begins,
+                                int32_t* ends, uint64_t* c_table, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && experts_per_rank >= 1, "ep_wait_build: bad sizes");
+  SY_REQUIRE(arrive_flags && meta && y_dst && begins && ends && c_table, "ep_wait_build: null pointer");
+  ReturnTargets rt;
+  for (int s = 0; s < n_ranks; ++s) {
+    rt.y[s] = static_cast<unsigned char*>(y_dst[s]);
+    rt.flag[s] = nullptr;
+    SY_REQUIRE(rt.y[s], "ep_wait_build: null result buffer for rank %d", s);
+  }
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  ep_wait_build_kernel<<<1, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      arrive_flags, meta, experts_per_rank, n_ranks, capacity, rt, out_row_bytes, epoch, begins, ends,
+      reinterpret_cast<unsigned long long*>(c_table), status);
+  return check_cuda(cudaGetLastError(), "ep_wait_build launch");
+}
+
+extern "C" int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, int epoch, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && flag_dst, "ep_signal: bad arguments");
+  ReturnTargets rt;
+  for (int s = 0; s < n_ranks; ++s) {
+    rt.y[s] = nullptr;
+    rt.flag[s] = flag_dst[s];
+    SY_REQUIRE(rt.flag[s], "ep_signal: null flag for rank %d", s);
+  }
+  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(rt, n_ranks, epoch);
+  return check_cuda(cudaGetLastError(), "ep_signal launch");
+}
+
+extern "C" int sy_ep_wait(const int32_t* flags, int n, int epoch, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(flags && n >= 1 && n <= 32, "ep_wait: bad arguments");
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status);
+  return check_cuda(cudaGetLastError(), "ep_wait launch");
+}
+
+// ---- CUDA IPC helpers: how the ranks' windows are mapped into one another (set-up time) ----
+extern "C" int sy_ipc_export(void* ptr, unsigned char* handle64, uint64_t* offset_out) {
+  using namespace sy;
+  SY_REQUIRE(ptr && handle64 && offset_out, "ipc_export: null pointer");
+  // the handle names the whole allocation that contains ptr; find its base
+  typedef int (*RangeFn)(unsigned long long*, size_t*, unsigned long long);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  SY_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q));
+  if (q != cudaDriverEntryPointSuccess || !fn) return fail(SY_ERR_CUDA, "ipc_export: no cuMemGetAddressRange");
+  unsigned long long base = 0;
+  size_t size = 0;
+  int r = reinterpret_cast<RangeFn>(fn)(&base, &size, (unsigned long long)(uintptr_t)ptr);
+  if (r != 0) return fail(SY_ERR_CUDA, "ipc_export: cuMemGetAddressRange failed (%d)", r);
+  cudaIpcMemHandle_t h;
+  SY_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>((uintptr_t)base)));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *offset_out = (uint64_t)((uintptr_t)ptr - (uintptr_t)base);
+  return SY_OK;
+}
+
+extern "C" int sy_ipc_open(const unsigned char* handle64, uint64_t offset, void** ptr_out) {
+  using namespace sy;
+  SY_REQUIRE(handle64 && ptr_out, "ipc_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* base = nullptr;
+  SY_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr_out = static_cast<unsigned char*>(base) + offset;
+  return SY_OK;
+}
+
+extern "C" int sy_ipc_close(void* ptr, uint64_t offset) {
+  using namespace sy;
+  if (!ptr) return SY_OK;
+  SY_CUDA(cudaIpcCloseMemHandle(static_cast<unsigned char*>(ptr) - offset));
+  return SY_OK;
+}

@@ -117,7 +117,7 @@ template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict__ A,
                  const int* __restrict__ a_rows, const int* __restrict__ begins, const int* __restrict__ ends, int E,
-                 int weight_sets, int Nout, int K, const T* __restrict__ scale, T* __restrict__ C,
+                 int group_div, int Nout, int K, const T* __restrict__ scale, T* __restrict__ C,
                  const unsigned long long* __restrict__ c_table, int* status) {
   using S = Shape<PAIR>;
   constexpr int BN = S::BN, STAGES = S::STAGES, STAGE_BYTES = S::STAGE_BYTES;
@@ -198,7 +198,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
         const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
-        const int y0 = (tile.e % weight_sets) * Nfull + tile.cb * COLS;
+        const int y0 = (tile.e / group_div) * Nfull + tile.cb * COLS;  // group g uses weights g / group_div
         const int y1 = SWIGLU ? y0 + Nout : y0 + S::BOX_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES, use = it / STAGES;
@@ -493,8 +493,8 @@ struct GroupedArgs {
   const void* B;
   const int32_t* begins;   // [groups] first row of each group
   const int32_t* ends;     // [groups] one past its last row
-  int groups;              // number of groups (an expert's slice; or sender x local expert)
-  int weight_sets;         // group g uses weights B[g % weight_sets]
+  int groups;              // number of groups (an expert's slice; or local expert x sender)
+  int group_div;           // group g uses weights B[g / group_div]
   int n_out, k_dim;
   const void* scale;
   void* C;
@@ -511,8 +511,8 @@ static int launch_gemm(const GroupedArgs& a) {
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
   CUtensorMap map;
-  rc = weight_map(&map, a.B, (uint64_t)a.weight_sets * (SWIGLU ? 2 : 1) * a.n_out, (uint64_t)a.k_dim, a.dtype,
-                  Shape<PAIR>::BOX_ROWS);
+  rc = weight_map(&map, a.B, (uint64_t)(a.groups / a.group_div) * (SWIGLU ? 2 : 1) * a.n_out, (uint64_t)a.k_dim,
+                  a.dtype, Shape<PAIR>::BOX_ROWS);
   if (rc != SY_OK) return rc;
   auto kern = gemm_umma_kernel<T, SWIGLU, SCALE, PAIR>;
   static std::atomic<int> configured[MAX_DEVICES];
@@ -523,7 +523,7 @@ static int launch_gemm(const GroupedArgs& a) {
     configured[dev].store(1, std::memory_order_release);
   }
   kern<<<sms, GM_THREADS, GM_SMEM, a.stream>>>(map, static_cast<const T*>(a.A), a.a_rows, a.begins, a.ends, a.groups,
-                                               a.weight_sets, a.n_out, a.k_dim, static_cast<const T*>(a.scale),
+                                               a.group_div, a.n_out, a.k_dim, static_cast<const T*>(a.scale),
                                                static_cast<T*>(a.C), a.c_table, status);
   return check_cuda(cudaGetLastError(), "grouped tcgen05 launch");
 }
@@ -538,7 +538,8 @@ static int dispatch_gemm(const GroupedArgs& a, int swiglu) {
 // Shared argument checks and dtype dispatch of the tensor-core entry points.
 int grouped_umma(bool pair, const char* name, const GroupedArgs& a, int rows, int swiglu) {
   SY_REQUIRE(rows >= 0 && a.groups >= 1 && a.groups <= GM_MAX_E, "%s: 1..%d groups (got %d)", name, GM_MAX_E, a.groups);
-  SY_REQUIRE(a.weight_sets >= 1 && a.weight_sets <= a.groups, "%s: bad number of weight sets %d", name, a.weight_sets);
+  SY_REQUIRE(a.group_div >= 1 && a.groups % a.group_div == 0, "%s: %d groups do not divide by %d", name, a.groups,
+             a.group_div);
   SY_REQUIRE(a.k_dim > 0 && a.k_dim % 8 == 0, "%s: k_dim must be a multiple of 8 (got %d)", name, a.k_dim);
   SY_REQUIRE(a.n_out > 0 && a.n_out % 8 == 0, "%s: n_out must be a multiple of 8 (got %d)", name, a.n_out);
   SY_REQUIRE(!(swiglu && a.scale), "%s: swiglu and scale are separate epilogues", name);
@@ -561,7 +562,7 @@ extern "C" int sy_prof_read(long long* out, int blocks) {
 extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                                int dtype, void* stream) {
-  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, n_experts, n_out, k_dim,
+  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, 1, n_out, k_dim,
                     scale, C, nullptr, dtype, static_cast<cudaStream_t>(stream)};
   return sy::grouped_umma(true, "grouped_gemm", a, rows, swiglu);
 }
@@ -569,16 +570,16 @@ extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void*
 extern "C" int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                                int dtype, void* stream) {
-  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, n_experts, n_out, k_dim,
+  sy::GroupedArgs a{A, a_rows, B, offsets, offsets ? offsets + 1 : nullptr, n_experts, 1, n_out, k_dim,
                     scale, C, nullptr, dtype, static_cast<cudaStream_t>(stream)};
   return sy::grouped_umma(false, "grouped_gemv", a, rows, swiglu);
 }
 
 extern "C" int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, const int32_t* ends,
-                                   int n_groups, int weight_sets, int rows_bound, int n_out, int k_dim, int swiglu,
+                                   int n_groups, int groups_per_expert, int rows_bound, int n_out, int k_dim, int swiglu,
                                    const void* scale, void* C, const uint64_t* c_table, int dtype, int compute_shape,
                                    void* stream) {
-  sy::GroupedArgs a{A, nullptr, B, begins, ends, n_groups, weight_sets, n_out, k_dim, scale, C,
+  sy::GroupedArgs a{A, nullptr, B, begins, ends, n_groups, groups_per_expert, n_out, k_dim, scale, C,
                     reinterpret_cast<const unsigned long long*>(c_table), dtype, static_cast<cudaStream_t>(stream)};
   return sy::grouped_umma(compute_shape != 0, "grouped_segments", a, rows_bound, swiglu);
 }

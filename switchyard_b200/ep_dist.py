@@ -1,0 +1,164 @@
+"""Expert parallelism with one process per GPU (torchrun-style), over this library's
+device-driven transport (csrc/ep.cu).
+
+`ep.ExpertParallel` mirrors the reference: one process drives all GPUs with a thread per rank,
+events between streams and one host read per layer. `DistributedExpertParallel` is the form for
+one process per GPU: every rank maps every other rank's window (CUDA IPC), a layer is ten
+launches on the rank's stream, and the host never reads anything back:
+
+    router GEMM, route, sort                      (local tokens, global expert ids)
+    ep_dispatch                                   rows -> owners' mailboxes, arrival flags
+    ep_wait_build                                 wait for all senders, build row groups
+    grouped kernel x2                             experts; results stored straight into the senders' y
+    ep_signal                                     return flags
+    ep_wait, combine                              wait for all owners, sum in expert order
+
+The arithmetic per row and the order of the combine are those of the single-GPU layer with the
+same `mode`, so every rank's output is bit-identical to `kernels.moe_layer` on its own tokens.
+
+torch.distributed is used at set-up only (to exchange the 64-byte IPC handles) and never on the
+data path."""
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import _lib, kernels
+
+_ALIGN = 256
+
+
+def _up(n, a=_ALIGN):
+    return (n + a - 1) // a * a
+
+
+def window_layout(n_ranks, experts_per_rank, capacity, y_rows, hidden, elem_bytes):
+    """Byte offsets of the regions of a rank's window. Every rank uses the same layout, so a
+    peer's region is its mapped base plus these offsets.
+      arrive [R] int32   arrival flag per sender       ret [R] int32   return flag per owner
+      done   [1] int32   dispatch's block counter      meta [R][per+3] int32
+      w      [R][cap]    router weights per sender     x    [R][cap][H] rows per sender
+      y      [y_rows][H] results for this rank's own sorted rows"""
+    off, lay = 0, {}
+    for name, nbytes in (("arrive", 4 * n_ranks), ("ret", 4 * n_ranks), ("done", 4),
+                         ("meta", 4 * n_ranks * (experts_per_rank + 3)),
+                         ("w", n_ranks * capacity * elem_bytes),
+                         ("x", n_ranks * capacity * hidden * elem_bytes),
+                         ("y", y_rows * hidden * elem_bytes)):
+        lay[name] = off
+        off += _up(nbytes)
+    lay["total"] = off
+    return lay
+
+
+def _ptr_array(values):
+    arr = (ctypes.c_void_p * len(values))(*values)
+    return arr
+
+
+class DistributedExpertParallel:
+    """One rank of an expert-parallel MoE layer; construct it on every rank of `group`
+    (collective). max_tokens bounds the tokens any single rank passes to layer()."""
+
+    def __init__(self, num_experts, top_k, norm_topk_prob, hidden, inter, max_tokens, dtype=torch.float16,
+                 mode="gemv", device=None, group=None, logit_bias=None):
+        self.group = group
+        self.rank, self.R = dist.get_rank(group), dist.get_world_size(group)
+        assert num_experts % self.R == 0, "experts must split evenly over the ranks"
+        assert mode in ("gemv", "gemm"), "the distributed layer takes an explicit mode"
+        self.E, self.per, self.k, self.norm = num_experts, num_experts // self.R, top_k, norm_topk_prob
+        self.H, self.I, self.dtype, self.mode = hidden, inter, dtype, mode
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.max_tokens = max_tokens
+        self.cap = max_tokens * top_k          # a sender's whole batch may go to one rank
+        self.y_rows = max_tokens * top_k
+        self.elem = torch.empty(0, dtype=dtype).element_size()
+        self.bias = None if logit_bias is None else logit_bias.to(device=self.device, dtype=dtype)
+        self.lib = _lib.load()
+        self.ext = kernels.ext()
+        self.epoch = 0
+        lay = self.layout = window_layout(self.R, self.per, self.cap, self.y_rows, hidden, self.elem)
+
+        torch.cuda.set_device(self.device)
+        self.window = torch.zeros(lay["total"], dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+        handle = (ctypes.c_ubyte * 64)()
+        offset = ctypes.c_uint64(0)
+        _lib.check(self.lib.sy_ipc_export(self.window.data_ptr(), handle, ctypes.byref(offset)), "ipc_export")
+        mine = (bytes(handle), int(offset.value))
+        everyone = [None] * self.R
+        dist.all_gather_object(everyone, mine, group=group)
+        self.bases, self._opened = [], []
+        for r, (hbytes, off) in enumerate(everyone):
+            if r == self.rank:
+                self.bases.append(self.window.data_ptr())
+                continue
+            p = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(hbytes)
+            _lib.check(self.lib.sy_ipc_open(buf, off, ctypes.byref(p)), "ipc_open")
+            self.bases.append(p.value)
+            self._opened.append((p.value, off))
+
+        me, cap, H, eb = self.rank, self.cap, hidden, self.elem
+        # where this rank's rows for receiver d go: slot `me` of d's mailbox
+        self.x_dst = _ptr_array([b + lay["x"] + me * cap * H * eb for b in self.bases])
+        self.w_dst = _ptr_array([b + lay["w"] + me * cap * eb for b in self.bases])
+        self.meta_dst = _ptr_array([b + lay["meta"] + me * (self.per + 3) * 4 for b in self.bases])
+        self.arrive_dst = _ptr_array([b + lay["arrive"] + me * 4 for b in self.bases])
+        self.ret_dst = _ptr_array([b + lay["ret"] + me * 4 for b in self.bases])
+        self.y_dst = _ptr_array([b + lay["y"] for b in self.bases])
+        base = self.window.data_ptr()
+        self.p_arrive, self.p_ret, self.p_done = base + lay["arrive"], base + lay["ret"], base + lay["done"]
+        self.p_meta, self.p_w, self.p_x = base + lay["meta"], base + lay["w"], base + lay["x"]
+        self.y = self.window[lay["y"]:lay["y"] + self.y_rows * H * eb].view(dtype).view(self.y_rows, H)
+        # local scratch of the compute phase
+        G = self.R * self.per
+        self.groups = torch.zeros(2 * G, dtype=torch.int32, device=self.device)
+        self.c_table = torch.zeros(G, dtype=torch.int64, device=self.device)
+        self.act = torch.empty(self.R * cap, inter, dtype=dtype, device=self.device)
+        dist.barrier(group=group)  # every window is mapped everywhere before the first layer
+
+    def layer(self, h, router, gate_up, down):
+        """h [N,H] this rank's tokens (N <= max_tokens, may be 0); router [E,H] (replicated);
+        gate_up [E/R,2I,H], down [E/R,H,I]: this rank's experts. Returns [N,H]. Collective:
+        every rank must call it once per layer, in the same order."""
+        N = h.shape[0]
+        if N > self.max_tokens:
+            raise RuntimeError(f"layer: {N} tokens exceed max_tokens={self.max_tokens}")
+        lib, ext, R, per, cap, H = self.lib, self.ext, self.R, self.per, self.cap, self.H
+        self.epoch += 1
+        epoch = self.epoch
+        h = h.contiguous()
+        logits = F.linear(h, router)
+        if self.bias is not None:
+            logits = logits + self.bias
+        idx, w = ext.route(logits.contiguous(), self.k, self.norm)
+        counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, self.E)
+        M = N * self.k
+        code = _lib.SY_DTYPE_F16 if self.dtype == torch.float16 else _lib.SY_DTYPE_BF16
+        shape = 1 if self.mode == "gemm" else 0
+        with kernels._Device(self.device) as stream:
+            _lib.check(lib.sy_ep_dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M, per,
+                                          R, H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst, self.arrive_dst,
+                                          self.p_done, epoch, stream), "ep_dispatch")
+            G = R * per
+            begins, ends = self.groups.data_ptr(), self.groups.data_ptr() + 4 * G
+            _lib.check(lib.sy_ep_wait_build(self.p_arrive, self.p_meta, per, R, cap, self.y_dst, H * self.elem, epoch,
+                                            begins, ends, self.c_table.data_ptr(), stream), "ep_wait_build")
+            _lib.check(lib.sy_grouped_segments(self.p_x, gate_up.data_ptr(), begins, ends, G, R, R * cap, self.I, H, 1,
+                                               None, self.act.data_ptr(), None, code, shape, stream), "grouped_segments")
+            _lib.check(lib.sy_grouped_segments(self.act.data_ptr(), down.data_ptr(), begins, ends, G, R, R * cap, H,
+                                               self.I, 0, self.p_w, None, self.c_table.data_ptr(), code, shape, stream),
+                       "grouped_segments")
+            _lib.check(lib.sy_ep_signal(self.ret_dst, R, epoch, stream), "ep_signal")
+            _lib.check(lib.sy_ep_wait(self.p_ret, R, epoch, stream), "ep_wait")
+        return ext.combine(self.y, pos_of, idx, N)
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p, off in self._opened:
+            self.lib.sy_ipc_close(p, off)
+        self._opened = []
