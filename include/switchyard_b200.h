@@ -131,32 +131,37 @@ int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, con
                         int groups_per_expert, int rows_bound, int n_out, int k_dim, int swiglu, const void* scale,
                         void* C, const uint64_t* c_table, int dtype, int compute_shape, void* stream);
 
+/* Epochs: every rank keeps one int32 layer counter in its own device memory (zero-initialised,
+ * passed as epoch_counter). sy_ep_dispatch advances it and publishes the new value in the
+ * receivers' arrival flags; the other entry points of the same layer read it. The host passes
+ * no per-layer value, so a whole layer can be captured in a CUDA graph and replayed. */
+
 /* ep_dispatch — sends every sorted row to the rank owning its expert: row i (expert in
  * [d*experts_per_rank, (d+1)*experts_per_rank)) is copied from h[token[i]] to row
  * i - offsets[d*experts_per_rank] of x_dst[d], its router weight to w_dst[d]; meta_dst[d] gets
  * experts_per_rank+1 rebased offsets, the segment's first row and its row count; finally
- * *flag_dst[d] = epoch (release, system scope) for every d. done_counter: one zero-initialised
+ * *flag_dst[d] = ++*epoch_counter (release, system scope) for every d. done_counter: one zero-initialised
  * int of this rank's memory. Rows past `capacity` of a mailbox are dropped and reported through
  * the status word. m == 0 still publishes (empty) mailboxes. */
 int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
                    int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
                    void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* done_counter,
-                   int epoch, void* stream);
+                   int32_t* epoch_counter, void* stream);
 
-/* ep_wait_build — waits (bounded, 2 s) until arrive_flags[s] >= epoch for every sender, then
+/* ep_wait_build — waits (bounded, 2 s) until arrive_flags[s] >= *epoch_counter for every sender, then
  * builds the row groups of this rank's mailbox (group e*n_ranks + s = sender s's rows of local
  * expert e; sender s's rows start at s*capacity) and c_table (where each group's results go:
  * y_dst[s] + (first row of the segment in the sender's sort + rebased offset) * out_row_bytes). */
 int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
-                     int capacity, void* const* y_dst, int out_row_bytes, int epoch, int32_t* begins,
-                     int32_t* ends, uint64_t* c_table, void* stream);
+                     int capacity, void* const* y_dst, int out_row_bytes, const int32_t* epoch_counter,
+                     int32_t* begins, int32_t* ends, uint64_t* c_table, void* stream);
 
-/* ep_signal — *flag_dst[s] = epoch (release, system scope) for every s, after everything
+/* ep_signal — *flag_dst[s] = *epoch_counter (release, system scope) for every s, after everything
  * enqueued before it on `stream` (the results written into the senders' memory) is done. */
-int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, int epoch, void* stream);
+int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t* epoch_counter, void* stream);
 
-/* ep_wait — waits (bounded, 2 s) until flags[i] >= epoch for i < n (n <= 32). */
-int sy_ep_wait(const int32_t* flags, int n, int epoch, void* stream);
+/* ep_wait — waits (bounded, 2 s) until flags[i] >= *epoch_counter for i < n (n <= 32). */
+int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, void* stream);
 
 /* ipc_export / ipc_open / ipc_close — map one rank's window into another process (CUDA IPC).
  * export: 64-byte handle of the allocation containing ptr and ptr's offset in it.

@@ -69,15 +69,32 @@ def run(args):
     stream = torch.cuda.Stream(dev)
     pass_no = [0]
 
+    # one CUDA graph per (T, weight set) holding the whole expert-parallel layer; every rank
+    # builds and replays them in the same order
+    graphs, outs = {}, {}
+    with torch.cuda.stream(stream):
+        for T in SWEEP:
+            for l, (router, gu, dn) in enumerate(layers):
+                ep.layer(hs[T], router, gu, dn)
+        stream.synchronize()
+        dist.barrier()
+        for T in SWEEP:
+            for l, (router, gu, dn) in enumerate(layers):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    outs[(T, l)] = ep.layer(hs[T], router, gu, dn)
+                graphs[(T, l)] = g
+    torch.cuda.synchronize()
+    dist.barrier()
+
     def step(timed, evs):
         for T in SWEEP:
             l = pass_no[0] % LAYERS
             pass_no[0] += 1
-            router, gu, dn = layers[l]
             if timed:
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream)
-            ep.layer(hs[T], router, gu, dn)
+            graphs[(T, l)].replay()
             if timed:
                 b.record(stream)
                 evs.append((T, l, a, b))
@@ -157,7 +174,7 @@ def run(args):
                        "tokens_per_gpu": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK,
                        "mode": mode, "parallelism": f"ep{world} (attention data-parallel)",
                        "l2": f"passes rotate over {LAYERS} resident weight sets",
-                       "timing": "CUDA events on each rank's stream, eager launches, max over ranks"},
+                       "timing": "CUDA events on each rank's stream around CUDA-graph replays of the whole layer, max over ranks"},
             "sweep": [{"tokens_per_gpu": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
                        "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
                        "tokens_per_s": T * world * args.steps / (per_T_ms[T] / 1e3)} for T in SWEEP],

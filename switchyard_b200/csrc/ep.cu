@@ -19,7 +19,10 @@
 //   signal      release-store of the epoch into every sender's return flag;
 //   wait        before the combine, one block waits for every owner's return flag.
 //
-// Flags only ever grow (the epoch is the layer counter), so nothing is reset between layers.
+// Flags only ever grow: the epoch is a per-rank layer counter kept in device memory (the
+// dispatch's last block advances it, the later kernels of the layer read it), so nothing is
+// reset between layers, the host passes no per-layer value, and a layer can be captured in a
+// CUDA graph and replayed. All ranks run the same sequence of layers, so their counters agree.
 // A mailbox is overwritten by layer n+1's dispatch only after its sender has passed layer n's
 // return wait, which the receiver signals after it has finished reading the mailbox.
 //
@@ -71,7 +74,7 @@ struct DispatchTargets {
 __global__ void __launch_bounds__(EP_THREADS)
 ep_dispatch_kernel(const uint4* __restrict__ h, const int* __restrict__ token, const unsigned short* __restrict__ wsorted,
                    const int* __restrict__ offsets, int M, int per, int R, int vec_per_row, int cap,
-                   DispatchTargets tg, int* done_counter, int epoch, int* status) {
+                   DispatchTargets tg, int* done_counter, int* epoch_counter, int* status) {
   __shared__ int s_seg[EP_MAX_RANKS + 1];
   __shared__ int s_last;
   if (threadIdx.x <= R) s_seg[threadIdx.x] = offsets[threadIdx.x * per];
@@ -108,9 +111,14 @@ ep_dispatch_kernel(const uint4* __restrict__ h, const int* __restrict__ token, c
   }
   __syncthreads();
   if (s_last) {
-    if (threadIdx.x == 0) *done_counter = 0;
+    const int epoch = *epoch_counter + 1;  // only this block reads it; every other block is done
     __threadfence_system();
     if (threadIdx.x < R) st_release_sys(tg.flag[threadIdx.x], epoch);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *done_counter = 0;
+      *epoch_counter = epoch;  // read by the layer's later kernels, which follow in stream order
+    }
   }
 }
 
@@ -122,9 +130,10 @@ struct ReturnTargets {
 // Groups are expert-major: group g = e * R + s holds sender s's rows for local expert e.
 __global__ void __launch_bounds__(EP_THREADS)
 ep_wait_build_kernel(const int* arrive_flags, const int* meta, int per, int R, int cap,
-                     ReturnTargets rt, int out_row_bytes, int epoch, int* __restrict__ begins, int* __restrict__ ends,
-                     unsigned long long* __restrict__ c_table, int* status) {
+                     ReturnTargets rt, int out_row_bytes, const int* epoch_counter, int* __restrict__ begins,
+                     int* __restrict__ ends, unsigned long long* __restrict__ c_table, int* status) {
   __shared__ int s_ok;
+  const int epoch = *epoch_counter;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if (threadIdx.x < R && !wait_flag(arrive_flags + threadIdx.x, epoch)) {
@@ -143,12 +152,14 @@ ep_wait_build_kernel(const int* arrive_flags, const int* meta, int per, int R, i
   }
 }
 
-__global__ void ep_signal_kernel(ReturnTargets rt, int R, int epoch) {
+__global__ void ep_signal_kernel(ReturnTargets rt, int R, const int* epoch_counter) {
+  const int epoch = *epoch_counter;
   __threadfence_system();
   if (threadIdx.x < R) st_release_sys(rt.flag[threadIdx.x], epoch);
 }
 
-__global__ void ep_wait_kernel(const int* __restrict__ flags, int n, int epoch, int* status) {
+__global__ void ep_wait_kernel(const int* flags, int n, const int* epoch_counter, int* status) {
+  const int epoch = *epoch_counter;
   if (threadIdx.x < n && !wait_flag(flags + threadIdx.x, epoch)) *status = DS_TIMEOUT_FLAG;
 }
 
@@ -157,12 +168,13 @@ __global__ void ep_wait_kernel(const int* __restrict__ flags, int n, int epoch, 
 extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
                               int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
                               void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst,
-                              int32_t* done_counter, int epoch, void* stream) {
+                              int32_t* done_counter, int32_t* epoch_counter, void* stream) {
   using namespace sy;
   SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS, "ep_dispatch: 1..%d ranks (got %d)", EP_MAX_RANKS, n_ranks);
   SY_REQUIRE(m >= 0 && experts_per_rank >= 1 && capacity >= 1, "ep_dispatch: bad sizes");
   SY_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "ep_dispatch: row size must be a multiple of 16 bytes");
-  SY_REQUIRE(offsets && x_dst && w_dst && meta_dst && flag_dst && done_counter, "ep_dispatch: null pointer");
+  SY_REQUIRE(offsets && x_dst && w_dst && meta_dst && flag_dst && done_counter && epoch_counter,
+             "ep_dispatch: null pointer");
   SY_REQUIRE(m == 0 || (h && token && wsorted), "ep_dispatch: null pointer");
   DispatchTargets tg;
   for (int d = 0; d < n_ranks; ++d) {
@@ -181,16 +193,16 @@ extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* w
   int blocks = m < 1 ? 1 : (m < sms * 4 ? m : sms * 4);
   ep_dispatch_kernel<<<blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(h), token, static_cast<const unsigned short*>(wsorted), offsets, m, experts_per_rank,
-      n_ranks, row_bytes / 16, capacity, tg, done_counter, epoch, status);
+      n_ranks, row_bytes / 16, capacity, tg, done_counter, epoch_counter, status);
   return check_cuda(cudaGetLastError(), "ep_dispatch launch");
 }
 
 extern "C" int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
-                                int capacity, void* const* y_dst, int out_row_bytes, int epoch, int32_t* begins,
-                                int32_t* ends, uint64_t* c_table, void* stream) {
+                                int capacity, void* const* y_dst, int out_row_bytes, const int32_t* epoch_counter,
+                                int32_t* begins, int32_t* ends, uint64_t* c_table, void* stream) {
   using namespace sy;
   SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && experts_per_rank >= 1, "ep_wait_build: bad sizes");
-  SY_REQUIRE(arrive_flags && meta && y_dst && begins && ends && c_table, "ep_wait_build: null pointer");
+  SY_REQUIRE(arrive_flags && meta && y_dst && begins && ends && c_table && epoch_counter, "ep_wait_build: null pointer");
   ReturnTargets rt;
   for (int s = 0; s < n_ranks; ++s) {
     rt.y[s] = static_cast<unsigned char*>(y_dst[s]);
@@ -200,30 +212,30 @@ extern "C" int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
   ep_wait_build_kernel<<<1, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      arrive_flags, meta, experts_per_rank, n_ranks, capacity, rt, out_row_bytes, epoch, begins, ends,
+      arrive_flags, meta, experts_per_rank, n_ranks, capacity, rt, out_row_bytes, epoch_counter, begins, ends,
       reinterpret_cast<unsigned long long*>(c_table), status);
   return check_cuda(cudaGetLastError(), "ep_wait_build launch");
 }
 
-extern "C" int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, int epoch, void* stream) {
+extern "C" int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t* epoch_counter, void* stream) {
   using namespace sy;
-  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && flag_dst, "ep_signal: bad arguments");
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && flag_dst && epoch_counter, "ep_signal: bad arguments");
   ReturnTargets rt;
   for (int s = 0; s < n_ranks; ++s) {
     rt.y[s] = nullptr;
     rt.flag[s] = flag_dst[s];
     SY_REQUIRE(rt.flag[s], "ep_signal: null flag for rank %d", s);
   }
-  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(rt, n_ranks, epoch);
+  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(rt, n_ranks, epoch_counter);
   return check_cuda(cudaGetLastError(), "ep_signal launch");
 }
 
-extern "C" int sy_ep_wait(const int32_t* flags, int n, int epoch, void* stream) {
+extern "C" int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, void* stream) {
   using namespace sy;
-  SY_REQUIRE(flags && n >= 1 && n <= 32, "ep_wait: bad arguments");
+  SY_REQUIRE(flags && epoch_counter && n >= 1 && n <= 32, "ep_wait: bad arguments");
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
-  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch, status);
+  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch_counter, status);
   return check_cuda(cudaGetLastError(), "ep_wait launch");
 }
 

@@ -38,11 +38,12 @@ def window_layout(n_ranks, experts_per_rank, capacity, y_rows, hidden, elem_byte
     """Byte offsets of the regions of a rank's window. Every rank uses the same layout, so a
     peer's region is its mapped base plus these offsets.
       arrive [R] int32   arrival flag per sender       ret [R] int32   return flag per owner
-      done   [1] int32   dispatch's block counter      meta [R][per+3] int32
+      done   [1] int32   dispatch's block counter      epoch [1] int32  this rank's layer counter
+      meta   [R][per+3] int32
       w      [R][cap]    router weights per sender     x    [R][cap][H] rows per sender
       y      [y_rows][H] results for this rank's own sorted rows"""
     off, lay = 0, {}
-    for name, nbytes in (("arrive", 4 * n_ranks), ("ret", 4 * n_ranks), ("done", 4),
+    for name, nbytes in (("arrive", 4 * n_ranks), ("ret", 4 * n_ranks), ("done", 4), ("epoch", 4),
                          ("meta", 4 * n_ranks * (experts_per_rank + 3)),
                          ("w", n_ranks * capacity * elem_bytes),
                          ("x", n_ranks * capacity * hidden * elem_bytes),
@@ -78,7 +79,6 @@ class DistributedExpertParallel:
         self.bias = None if logit_bias is None else logit_bias.to(device=self.device, dtype=dtype)
         self.lib = _lib.load()
         self.ext = kernels.ext()
-        self.epoch = 0
         lay = self.layout = window_layout(self.R, self.per, self.cap, self.y_rows, hidden, self.elem)
 
         torch.cuda.set_device(self.device)
@@ -111,6 +111,7 @@ class DistributedExpertParallel:
         self.y_dst = _ptr_array([b + lay["y"] for b in self.bases])
         base = self.window.data_ptr()
         self.p_arrive, self.p_ret, self.p_done = base + lay["arrive"], base + lay["ret"], base + lay["done"]
+        self.p_epoch = base + lay["epoch"]
         self.p_meta, self.p_w, self.p_x = base + lay["meta"], base + lay["w"], base + lay["x"]
         self.y = self.window[lay["y"]:lay["y"] + self.y_rows * H * eb].view(dtype).view(self.y_rows, H)
         # local scratch of the compute phase
@@ -128,8 +129,7 @@ class DistributedExpertParallel:
         if N > self.max_tokens:
             raise RuntimeError(f"layer: {N} tokens exceed max_tokens={self.max_tokens}")
         lib, ext, R, per, cap, H = self.lib, self.ext, self.R, self.per, self.cap, self.H
-        self.epoch += 1
-        epoch = self.epoch
+        epoch = self.p_epoch  # the layer counter lives on the device: nothing here changes per layer
         h = h.contiguous()
         logits = F.linear(h, router)
         if self.bias is not None:
