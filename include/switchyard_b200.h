@@ -65,6 +65,26 @@ int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n
                       int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
                       void* scratch, size_t scratch_bytes, void* stream);
 
+/* sort_by_expert_static — no counterpart in the reference. The same sort, same outputs bit for
+ * bit, for callers that are not allowed to allocate device memory while they run and so
+ * cannot provide scratch: a server that has handed all free HBM to its own arena (cudaMalloc
+ * would fail), a plugin whose host forbids allocation on the request path. The table of
+ * per-block expert counts is a 128 KiB array inside the library image, present on every GPU
+ * that loads the library until the process exits. This entry point calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *   - At most 1 048 576 choices (m) per call and 256 experts; more is rejected with
+ *     SY_ERR_ARGUMENT (use sy_sort_by_expert with your own scratch).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current): make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array. It needs no clearing between calls (every
+ *     entry read is written earlier in the same call), but two calls with m > 8192 that overlap
+ *     on the GPU (different streams) race on it: keep them on one stream or serialise them.
+ *     Calls with m <= 8192 sort in one block and do not touch the array. */
+int sy_sort_by_expert_static(const int32_t* idx, const void* w, int m, int top_k, int n_experts, int dtype,
+                             int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                             void* stream);
+
 /* grouped_gemv — replaces `grouped_gemv` (moe_kernels.cu:385-415, kernel l.306-383): the decode
  * path, for batches with few rows per expert, where the layer is bound by reading weights.
  * For every sorted row r of expert e (offsets[e] <= r < offsets[e+1]):

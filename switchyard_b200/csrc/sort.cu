@@ -14,6 +14,8 @@
 //
 // Replaces the reference's one-block-per-expert sort (switchyard/csrc/moe_kernels.cu:94-157),
 // which reads the whole list once per expert and calls torch for the prefix sum in between.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sy {
@@ -252,4 +254,65 @@ extern "C" int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int t
              ? launch_sort<__half>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch, s)
              : launch_sort<__nv_bfloat16>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch,
                                           s);
+}
+
+// ---- sort_by_expert_static: the same sort for callers that cannot hand over scratch ----------
+// Some hosts of this library must not allocate device memory once they are running: a serving
+// process that has given every free byte of HBM to its own cache arena (a later cudaMalloc
+// simply fails), or a plugin whose host forbids allocation calls on the request path. For them
+// the multi-block sort's table of per-block expert counts lives in the library image itself.
+namespace sy {
+
+constexpr int SORT_STATIC_MAX_M = 1 << 20;  // choices per call (131 072 tokens x top-8)
+
+// [SORT_MAX_BLOCKS][SORT_MAX_E] ints = 128 KiB, held by every GPU that loads the library until
+// the process exits. In host code this name is only a handle for cudaGetSymbolAddress.
+static __device__ __align__(256) int g_sort_static_table[SORT_MAX_BLOCKS * SORT_MAX_E];
+
+static int* g_sort_static_ptr[MAX_DEVICES];
+static std::mutex g_sort_static_mutex;
+
+// Device address of the table on the CURRENT device, looked up once per device.
+static int sort_static_table(int** out) {
+  int dev = -1;
+  SY_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) return fail(SY_ERR_ARGUMENT, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_sort_static_mutex);
+  if (!g_sort_static_ptr[dev]) {
+    void* p = nullptr;
+    SY_CUDA(cudaGetSymbolAddress(&p, g_sort_static_table));
+    g_sort_static_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_sort_static_ptr[dev];
+  return SY_OK;
+}
+
+}  // namespace sy
+
+extern "C" int sy_sort_by_expert_static(const int32_t* idx, const void* w, int m, int top_k, int n_experts,
+                                        int dtype, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
+                                        int32_t* pos_of, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(m >= 0 && top_k >= 1, "sort_by_expert_static: bad sizes (m=%d, k=%d)", m, top_k);
+  SY_REQUIRE(m <= SORT_STATIC_MAX_M, "sort_by_expert_static: at most %d choices per call (got %d); use "
+             "sy_sort_by_expert with caller-provided scratch beyond that", SORT_STATIC_MAX_M, m);
+  SY_REQUIRE(n_experts >= 1 && n_experts <= SORT_MAX_E, "sort_by_expert_static: at most %d experts (got %d)",
+             SORT_MAX_E, n_experts);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "sort_by_expert_static: dtype must be f16 or bf16");
+  SY_REQUIRE(counts && offsets, "sort_by_expert_static: null output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (m == 0) {
+    SY_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, s));
+    SY_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (n_experts + 1), s));
+    return SY_OK;
+  }
+  SY_REQUIRE(idx && w && token && wsorted && pos_of, "sort_by_expert_static: null pointer");
+  int* table = nullptr;
+  int rc = sort_static_table(&table);  // first call on a device: symbol look-up (keep it out of stream capture)
+  if (rc != SY_OK) return rc;
+  // Nothing in the table has to start at zero: launch 1 writes every [block][expert] entry that
+  // launch 2 reads. What is left from the previous call is overwritten or never looked at.
+  return dtype == SY_DTYPE_F16
+             ? launch_sort<__half>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, table, s)
+             : launch_sort<__nv_bfloat16>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, table, s);
 }
