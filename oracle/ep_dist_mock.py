@@ -1,0 +1,236 @@
+"""A host-memory stand-in for the device side of switchyard_b200.ep_dist. TEST INFRASTRUCTURE ONLY.
+
+`DistributedExpertParallel` talks to its device through a small backend object: the C-ABI entry
+points of the transport (`sy_ep_dispatch`, `sy_ep_wait_build`, `sy_grouped_segments`,
+`sy_ep_signal`, `sy_ep_wait`, `sy_ipc_*`), the routing / sort / combine wrappers, and memory.
+`MockBackend` provides the same names over HOST shared memory: a rank's window is a file in
+/dev/shm that the other processes map (the stand-in for CUDA IPC), "kernels" are numpy / torch
+code working on raw addresses, and flag waits are bounded polling loops. With it the product's
+host-side protocol (window layout, pointer tables, argument order, epochs, buffer reuse) runs in
+real separate processes over gloo, without a GPU.
+
+The arithmetic follows the kernel rules of oracle/moe_oracle.py, one row at a time, so that a
+row's result does not depend on how rows are grouped (the property the GPU kernels have)."""
+
+import ctypes
+import os
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+from . import moe_oracle as mo
+
+WAIT_SECONDS = 30.0
+
+
+def _view(addr, count, dtype):
+    """numpy view of `count` items of `dtype` at raw address `addr`."""
+    nbytes = count * np.dtype(dtype).itemsize
+    buf = (ctypes.c_ubyte * nbytes).from_address(int(addr))
+    return np.frombuffer(buf, dtype=dtype, count=count)
+
+
+def _addr(p):
+    return p.value if isinstance(p, ctypes.c_void_p) else (0 if p is None else int(p))
+
+
+def _torch16(addr, rows, cols, dtype):
+    a = _view(addr, rows * cols, np.int16)
+    return torch.from_numpy(a).view(dtype).view(rows, cols)
+
+
+def _row_linear(x_row, W):
+    """One row through nn.Linear weights in float32: the same arithmetic whatever the batch."""
+    return (W.float() @ x_row.float())
+
+
+class _Lib:
+    """The transport entry points, on host memory."""
+
+    def __init__(self):
+        self.maps = {}   # address -> tensor keeping a peer mapping alive
+        self.error = b""
+
+    def sy_last_error(self):
+        return self.error
+
+    # ---- the stand-in for CUDA IPC: a window is a file in /dev/shm
+    def sy_ipc_export(self, ptr, handle, offset_ref):
+        path = MockBackend.paths[_addr(ptr)].encode()
+        assert len(path) < 64
+        for i in range(64):
+            handle[i] = path[i] if i < len(path) else 0
+        offset_ref._obj.value = 0
+        return 0
+
+    def sy_ipc_open(self, handle, offset, out_ref):
+        path = bytes(handle).split(b"\0")[0].decode()
+        t = torch.from_file(path, shared=True, size=os.path.getsize(path), dtype=torch.uint8)
+        self.maps[t.data_ptr()] = t
+        out_ref._obj.value = t.data_ptr() + offset
+        return 0
+
+    def sy_ipc_close(self, ptr, offset):
+        self.maps.pop(int(ptr) - offset, None)
+        return 0
+
+    # ---- transport
+    def sy_ep_dispatch(self, h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
+                       done_counter, epoch_counter, stream):
+        off = _view(offsets, R * per + 1, np.int32)
+        tok = _view(token, m, np.int32) if m else np.zeros(0, np.int32)
+        wsrc = _view(wsorted, m, np.int16) if m else np.zeros(0, np.int16)
+        for d in range(R):
+            a, b = int(off[d * per]), int(off[(d + 1) * per])
+            n = min(b - a, cap)
+            meta = _view(meta_dst[d], per + 3, np.int32)
+            meta[:per + 1] = off[d * per:(d + 1) * per + 1] - a
+            meta[per + 1], meta[per + 2] = a, n
+            if n:
+                src_rows = tok[a:a + n]
+                dst = _view(x_dst[d], n * row_bytes, np.uint8).reshape(n, row_bytes)
+                hsrc = _view(h, (int(src_rows.max()) + 1) * row_bytes, np.uint8).reshape(-1, row_bytes)
+                dst[:] = hsrc[src_rows]
+                _view(w_dst[d], n, np.int16)[:] = wsrc[a:a + n]
+        ep = _view(epoch_counter, 1, np.int32)
+        epoch = int(ep[0]) + 1
+        for d in range(R):
+            _view(flag_dst[d], 1, np.int32)[0] = epoch
+        ep[0] = epoch
+        return 0
+
+    def _wait(self, flags, n, epoch):
+        f = _view(flags, n, np.int32)
+        deadline = time.time() + WAIT_SECONDS
+        while not (f >= epoch).all():
+            if time.time() > deadline:
+                self.error = b"mock: a flag never arrived"
+                return False
+            time.sleep(0.0005)
+        return True
+
+    def sy_ep_wait_build(self, arrive_flags, meta, per, R, cap, y_dst, out_row_bytes, epoch_counter, begins, ends,
+                         c_table, stream):
+        epoch = int(_view(epoch_counter, 1, np.int32)[0])
+        if not self._wait(arrive_flags, R, epoch):
+            return -3
+        m = _view(meta, R * (per + 3), np.int32).reshape(R, per + 3)
+        b, e, c = _view(begins, R * per, np.int32), _view(ends, R * per, np.int32), _view(c_table, R * per, np.uint64)
+        for g in range(R * per):
+            ex, s = divmod(g, R)
+            lo, hi = int(m[s, ex]), min(int(m[s, ex + 1]), cap)
+            b[g], e[g] = s * cap + lo, s * cap + max(hi, lo)
+            c[g] = int(y_dst[s]) + (int(m[s, per + 1]) + lo) * out_row_bytes
+        return 0
+
+    def sy_grouped_segments(self, A, B, begins, ends, n_groups, groups_per_expert, rows_bound, n_out, k_dim, swiglu,
+                            scale, C, c_table, dtype, compute_shape, stream):
+        dt = torch.float16 if dtype == 0 else torch.bfloat16
+        b, e = _view(begins, n_groups, np.int32), _view(ends, n_groups, np.int32)
+        n_full = 2 * n_out if swiglu else n_out
+        table = _view(c_table, n_groups, np.uint64) if _addr(c_table) else None
+        for g in range(n_groups):
+            lo, hi = int(b[g]), int(e[g])
+            if hi <= lo:
+                continue
+            W = _torch16(_addr(B) + (g // groups_per_expert) * n_full * k_dim * 2, n_full, k_dim, dt)
+            x = _torch16(_addr(A) + lo * k_dim * 2, hi - lo, k_dim, dt)
+            out_addr = int(table[g]) if table is not None else _addr(C) + lo * n_out * 2
+            out = _torch16(out_addr, hi - lo, n_out, dt)
+            sc = _torch16(_addr(scale) + lo * 2, hi - lo, 1, dt)[:, 0] if _addr(scale) else None
+            for r in range(hi - lo):
+                acc = _row_linear(x[r], W)[None]
+                if swiglu:
+                    out[r] = mo.epilogue_swiglu(acc[:, :n_out], acc[:, n_out:], dt)[0]
+                elif sc is not None:
+                    out[r] = mo.epilogue_scale(acc, sc[r:r + 1], dt)[0]
+                else:
+                    out[r] = acc.to(dt)[0]
+        return 0
+
+    def sy_ep_signal(self, flag_dst, R, epoch_counter, stream):
+        epoch = int(_view(epoch_counter, 1, np.int32)[0])
+        for s in range(R):
+            _view(flag_dst[s], 1, np.int32)[0] = epoch
+        return 0
+
+    def sy_ep_wait(self, flags, n, epoch_counter, stream):
+        return 0 if self._wait(flags, n, int(_view(epoch_counter, 1, np.int32)[0])) else -3
+
+
+class _Ext:
+    def route(self, logits, k, norm):
+        idx, w = mo.route_kernel_rule(logits, k, norm)
+        return [idx, w]
+
+    def sort_by_expert(self, idx, w, E):
+        return list(mo.sort_by_expert(idx, w, E))
+
+    def combine(self, y, pos_of, idx, n_tokens):
+        return mo.combine_expert_order(y, pos_of, idx, n_tokens)
+
+
+class _NullStream:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
+
+
+class MockBackend:
+    paths = {}  # window address -> its /dev/shm path (this process)
+
+    def __init__(self):
+        self.device = torch.device("cpu")
+        self.lib, self.ext = _Lib(), _Ext()
+        self._files = []
+
+    def zeros(self, n, dtype):
+        item = torch.empty(0, dtype=dtype).element_size()
+        fd, path = tempfile.mkstemp(prefix="sy_", dir="/dev/shm")
+        os.close(fd)
+        os.truncate(path, max(n * item, 1))
+        t = torch.from_file(path, shared=True, size=max(n, 1), dtype=dtype)[:n]
+        t.zero_()
+        self._files.append(path)
+        MockBackend.paths[t.data_ptr()] = path
+        return t
+
+    def empty(self, shape, dtype):
+        return torch.zeros(shape, dtype=dtype)
+
+    def linear(self, h, router):
+        return torch.stack([_row_linear(r, router) for r in h]).to(h.dtype) if h.shape[0] else h.new_zeros(0, router.shape[0])
+
+    def stream(self):
+        return _NullStream()
+
+    def sync(self):
+        pass
+
+    def cleanup(self):
+        for p in self._files:
+            try:
+                os.unlink(p)
+            except OSError:
+                pass
+
+
+def single_layer(h, router, gate_up, down, k, norm):
+    """The one-process comparand with the same row-at-a-time arithmetic as the mock kernels."""
+    be = MockBackend()
+    logits = be.linear(h, router)
+    idx, w = mo.route_kernel_rule(logits, k, norm)
+    counts, offsets, token, wsorted, pos_of = mo.sort_by_expert(idx, w, gate_up.shape[0])
+    M, I, H, dt = idx.numel(), gate_up.shape[1] // 2, down.shape[1], h.dtype
+    y = torch.zeros(M, H, dtype=dt)
+    off = offsets.tolist()
+    for e in range(gate_up.shape[0]):
+        for r in range(off[e], off[e + 1]):
+            acc = _row_linear(h[token[r]], gate_up[e])[None]
+            act = mo.epilogue_swiglu(acc[:, :I], acc[:, I:], dt)
+            y[r] = mo.epilogue_scale(_row_linear(act[0], down[e])[None], wsorted[r:r + 1], dt)[0]
+    return mo.combine_expert_order(y, pos_of, idx, h.shape[0])

@@ -59,31 +59,58 @@ def _ptr_array(values):
     return arr
 
 
+class CudaBackend:
+    """What the protocol below needs from a device: the C-ABI library, the torch-level kernel
+    wrappers, memory for the window and the scratch, the router GEMM and the current stream.
+    Tests substitute an object with the same attributes that keeps windows in host shared memory,
+    to run the host-side protocol (layout, pointer tables, call order) in CPU processes."""
+
+    def __init__(self, device):
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        torch.cuda.set_device(self.device)
+        self.lib = _lib.load()
+        self.ext = kernels.ext()
+
+    def zeros(self, n, dtype):
+        return torch.zeros(n, dtype=dtype, device=self.device)
+
+    def empty(self, shape, dtype):
+        return torch.empty(shape, dtype=dtype, device=self.device)
+
+    def linear(self, h, router):
+        return F.linear(h, router)
+
+    def stream(self):
+        return kernels._Device(self.device)
+
+    def sync(self):
+        torch.cuda.synchronize(self.device)
+
+
 class DistributedExpertParallel:
     """One rank of an expert-parallel MoE layer; construct it on every rank of `group`
     (collective). max_tokens bounds the tokens any single rank passes to layer()."""
 
     def __init__(self, num_experts, top_k, norm_topk_prob, hidden, inter, max_tokens, dtype=torch.float16,
-                 mode="gemv", device=None, group=None, logit_bias=None):
+                 mode="gemv", device=None, group=None, logit_bias=None, backend=None):
         self.group = group
         self.rank, self.R = dist.get_rank(group), dist.get_world_size(group)
         assert num_experts % self.R == 0, "experts must split evenly over the ranks"
         assert mode in ("gemv", "gemm"), "the distributed layer takes an explicit mode"
         self.E, self.per, self.k, self.norm = num_experts, num_experts // self.R, top_k, norm_topk_prob
         self.H, self.I, self.dtype, self.mode = hidden, inter, dtype, mode
-        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.backend = backend if backend is not None else CudaBackend(device)
+        self.device = self.backend.device
         self.max_tokens = max_tokens
         self.cap = max_tokens * top_k          # a sender's whole batch may go to one rank
         self.y_rows = max_tokens * top_k
         self.elem = torch.empty(0, dtype=dtype).element_size()
         self.bias = None if logit_bias is None else logit_bias.to(device=self.device, dtype=dtype)
-        self.lib = _lib.load()
-        self.ext = kernels.ext()
+        self.lib, self.ext = self.backend.lib, self.backend.ext
         lay = self.layout = window_layout(self.R, self.per, self.cap, self.y_rows, hidden, self.elem)
 
-        torch.cuda.set_device(self.device)
-        self.window = torch.zeros(lay["total"], dtype=torch.uint8, device=self.device)
-        torch.cuda.synchronize(self.device)
+        self.window = self.backend.zeros(lay["total"], torch.uint8)
+        self.backend.sync()
         handle = (ctypes.c_ubyte * 64)()
         offset = ctypes.c_uint64(0)
         _lib.check(self.lib.sy_ipc_export(self.window.data_ptr(), handle, ctypes.byref(offset)), "ipc_export")
@@ -116,9 +143,9 @@ class DistributedExpertParallel:
         self.y = self.window[lay["y"]:lay["y"] + self.y_rows * H * eb].view(dtype).view(self.y_rows, H)
         # local scratch of the compute phase
         G = self.R * self.per
-        self.groups = torch.zeros(2 * G, dtype=torch.int32, device=self.device)
-        self.c_table = torch.zeros(G, dtype=torch.int64, device=self.device)
-        self.act = torch.empty(self.R * cap, inter, dtype=dtype, device=self.device)
+        self.groups = self.backend.zeros(2 * G, torch.int32)
+        self.c_table = self.backend.zeros(G, torch.int64)
+        self.act = self.backend.empty((self.R * cap, inter), dtype)
         dist.barrier(group=group)  # every window is mapped everywhere before the first layer
 
     def layer(self, h, router, gate_up, down):
@@ -131,7 +158,7 @@ class DistributedExpertParallel:
         lib, ext, R, per, cap, H = self.lib, self.ext, self.R, self.per, self.cap, self.H
         epoch = self.p_epoch  # the layer counter lives on the device: nothing here changes per layer
         h = h.contiguous()
-        logits = F.linear(h, router)
+        logits = self.backend.linear(h, router)
         if self.bias is not None:
             logits = logits + self.bias
         idx, w = ext.route(logits.contiguous(), self.k, self.norm)
@@ -139,7 +166,7 @@ class DistributedExpertParallel:
         M = N * self.k
         code = _lib.SY_DTYPE_F16 if self.dtype == torch.float16 else _lib.SY_DTYPE_BF16
         shape = 1 if self.mode == "gemm" else 0
-        with kernels._Device(self.device) as stream:
+        with self.backend.stream() as stream:
             _lib.check(lib.sy_ep_dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M, per,
                                           R, H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst, self.arrive_dst,
                                           self.p_done, epoch, stream), "ep_dispatch")
@@ -157,7 +184,7 @@ class DistributedExpertParallel:
         return ext.combine(self.y, pos_of, idx, N)
 
     def close(self):
-        torch.cuda.synchronize(self.device)
+        self.backend.sync()
         dist.barrier(group=self.group)
         for p, off in self._opened:
             self.lib.sy_ipc_close(p, off)

@@ -1,0 +1,77 @@
+"""The one-process-per-rank expert-parallel protocol (switchyard_b200.ep_dist) in two and four
+real processes over gloo, without a GPU: the device side is replaced by the host-memory mock of
+oracle/ep_dist_mock.py (windows in /dev/shm mapped by the peers, polling flag waits), so what
+runs is the product's own host logic: window layout, pointer tables, argument order, device-side
+epochs, mailbox reuse over several layers, a rank with zero tokens. Every rank's output must
+equal the one-process layer computed with the same row-at-a-time arithmetic."""
+
+import socket
+
+import pytest
+import torch
+
+import cases
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, sizes_per_layer, out):
+    import torch.distributed as dist
+    from oracle import ep_dist_mock as mock
+    from switchyard_b200.ep_dist import DistributedExpertParallel
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    backend = mock.MockBackend()
+    try:
+        E, k, H, I = 16, 4, 32, 16
+        g = cases.gen(0)
+        router = torch.randn(E, H, generator=g).half()
+        gu = (torch.randn(E, 2 * I, H, generator=g) * 0.3).half()
+        dn = (torch.randn(E, H, I, generator=g) * 0.3).half()
+        per = E // world
+        ep = DistributedExpertParallel(E, k, False, H, I, max_tokens=max(max(s) for s in sizes_per_layer),
+                                       dtype=torch.float16, mode="gemv", backend=backend)
+        ok = True
+        for layer_no, sizes in enumerate(sizes_per_layer):
+            h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).half()
+            got = ep.layer(h, router, gu[rank * per:(rank + 1) * per].contiguous(), dn[rank * per:(rank + 1) * per].contiguous())
+            ok = ok and torch.equal(got, mock.single_layer(h, router, gu, dn, k, False))
+        ep.close()
+        out.put((rank, ok, ""))
+    except BaseException:
+        import traceback
+        out.put((rank, False, traceback.format_exc()))
+    finally:
+        backend.cleanup()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,sizes", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)]), (4, [(3, 7, 0, 2), (8, 8, 8, 8)])])
+def test_protocol_over_gloo_processes(world, sizes):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, ok, err in sorted(results):
+        assert not err, f"rank {rank}:\n{err}"
+        assert ok, f"rank {rank}: output differs from the one-process layer"
+
+
+def test_window_layout_is_aligned_and_disjoint():
+    from switchyard_b200.ep_dist import window_layout
+    lay = window_layout(8, 8, 2048, 2048, 2048, 2)
+    names = ["arrive", "ret", "done", "epoch", "meta", "w", "x", "y"]
+    offs = [lay[n] for n in names] + [lay["total"]]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert lay["x"] - lay["w"] >= 8 * 2048 * 2 and lay["y"] - lay["x"] >= 8 * 2048 * 2048 * 2
+    assert lay["total"] - lay["y"] >= 2048 * 2048 * 2
