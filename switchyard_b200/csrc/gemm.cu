@@ -24,7 +24,9 @@
 //               tensor memory; tcgen05.commit releases the stage / publishes the accumulators;
 //   warps 10-13 epilogue: tcgen05.ld of the accumulators (a thread owns one output column and
 //               walks the token rows), SwiGLU or router-weight scaling with the 16-bit
-//               rounding points, stores. It overlaps the next tile's main loop.
+//               rounding points, results staged in shared memory and written out as whole
+//               128/256-byte row segments (16 bytes per thread; the destination may be a peer
+//               GPU). It overlaps the next tile's main loop.
 //
 // An output element is a sum over k in instruction order that does not depend on which other
 // rows share the tile or on the tile's N, so a row's bits are the same on one GPU and inside
@@ -50,7 +52,9 @@ constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_GATHER_WARPS + GM_EPI_WARPS) * 32;
 constexpr int GM_MAX_E = 256;
 constexpr int GM_RING_BYTES = 192 * 1024;          // shared-memory ring of stages
-constexpr int GM_SMEM = GM_RING_BYTES + 1024;      // + room to align the ring to 1024
+constexpr int GM_EPI_ROWS = 64;                    // token rows the epilogue stages per pass
+constexpr int GM_EPI_BYTES = GM_EPI_ROWS * GM_BM * 2;  // staged output tile: 64 rows x 128 columns
+constexpr int GM_SMEM = GM_RING_BYTES + GM_EPI_BYTES + 1024;  // + room to align the ring to 1024
 constexpr uint64_t GM_WAIT_NS = 1000000000ull;
 
 // Two shapes of the same kernel.
@@ -137,6 +141,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* stages =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* out_tile = stages + GM_RING_BYTES;  // the epilogue's staged output rows
 
   const int col_blocks = (Nout + COLS - 1) / COLS;
   const int Nfull = SWIGLU ? 2 * Nout : Nout;
@@ -378,56 +383,134 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       // where this group's rows go: C, or (expert-parallel return) wherever c_table says the
       // group's first row lands, possibly in a peer GPU's memory
       T* __restrict__ Cg = c_table ? reinterpret_cast<T*>(c_table[tile.e]) - (size_t)s_begin[tile.e] * Nout : C;
-      if (PAIR || !SWIGLU) {
-        const int col0 = tile.cb * COLS + wrow;
-        const int col1 = col0 + GM_BM;  // the second accumulator's column (PAIR without SwiGLU)
-        for (int n0 = 0; n0 < tile.nvalid && alive; n0 += 8) {
-          uint32_t v0[8], v1[8];
-          tmem_ld_x8(taddr + n0, v0);
-          if (PAIR) tmem_ld_x8(taddr + BN + n0, v1);
-          tmem_ld_wait();
+      if (!c_table) {
+        // Local destination: every thread stores its own column's values directly (2 bytes per
+        // store, a warp covers 64 contiguous bytes of a row); L2 merges them, and the epilogue
+        // stays short enough to hide behind the next tile's main loop.
+        if (PAIR || !SWIGLU) {
+          const int col0 = tile.cb * COLS + wrow;
+          const int col1 = col0 + GM_BM;  // the second accumulator's column (PAIR without SwiGLU)
+          for (int n0 = 0; n0 < tile.nvalid && alive; n0 += 8) {
+            uint32_t v0[8], v1[8];
+            tmem_ld_x8(taddr + n0, v0);
+            if (PAIR) tmem_ld_x8(taddr + BN + n0, v1);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int row = tile.row0 + n0 + j;
-            if (n0 + j < tile.nvalid) {
-              const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
-              if (SWIGLU) {
-                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
-              } else if (SCALE) {
-                const T sc = scale[row];
-                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
-                if (PAIR && col1 < Nout) Cg[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
-              } else {
-                if (col0 < Nout) Cg[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
-                if (PAIR && col1 < Nout) Cg[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
+            for (int j = 0; j < 8; ++j) {
+              const int row = tile.row0 + n0 + j;
+              if (n0 + j < tile.nvalid) {
+                const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
+                if (SWIGLU) {
+                  if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
+                } else if (SCALE) {
+                  const T sc = scale[row];
+                  if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
+                  if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
+                } else {
+                  if (col0 < Nout) C[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
+                  if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
+                }
+              }
+            }
+          }
+        } else {
+          // one accumulator: lanes 0-63 hold the gate rows, lanes 64-127 the up rows of the same
+          // 64 output columns. Warps 2,3 pass their values to warps 0,1 through shared memory.
+          const int j64 = wrow & 63;
+          const int col = tile.cb * COLS + j64;
+          for (int n0 = 0; n0 < tile.nvalid; n0 += 8, ++chunk_no) {
+            uint32_t v[8];
+            if (alive) {
+              tmem_ld_x8(taddr + n0, v);
+              tmem_ld_wait();
+            }
+            float* slot = s_xch[chunk_no & 1][j64];
+            if (q >= 2 && alive) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
+            }
+            named_barrier_sync(2, GM_EPI_WARPS * 32);
+            if (q < 2 && alive) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int row = tile.row0 + n0 + j;
+                if (n0 + j < tile.nvalid && col < Nout)
+                  C[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
               }
             }
           }
         }
       } else {
-        // one accumulator: lanes 0-63 hold the gate rows, lanes 64-127 the up rows of the same
-        // 64 output columns. Warps 2,3 pass their values to warps 0,1 through shared memory.
-        const int j64 = wrow & 63;
-        const int col = tile.cb * COLS + j64;
-        for (int n0 = 0; n0 < tile.nvalid; n0 += 8, ++chunk_no) {
-          uint32_t v[8];
-          if (alive) {
-            tmem_ld_x8(taddr + n0, v);
-            tmem_ld_wait();
-          }
-          float* slot = s_xch[chunk_no & 1][j64];
-          if (q >= 2 && alive) {
+        // Destination given by c_table (usually a peer GPU): results go through a shared-memory
+        // tile so that memory is written in 16-byte pieces, a whole 128- or 256-byte row segment
+        // per group of threads, instead of one 2-byte store per thread (NVLink carries small
+        // stores poorly): up to GM_EPI_ROWS token rows x OC output columns per pass.
+        constexpr int OC = SWIGLU && !PAIR ? GM_BM / 2 : GM_BM;   // output columns per pass
+        constexpr int ORB = OC * 2;                               // bytes per staged row
+        constexpr int TPR = ORB / 16;                             // threads per row when copying out
+        constexpr int STORE_ACCS = (PAIR && !SWIGLU) ? 2 : 1;
+        const int et = threadIdx.x - (2 + GM_GATHER_WARPS) * 32;  // 0..127 among the epilogue threads
+#pragma unroll 1
+        for (int acc = 0; acc < STORE_ACCS; ++acc) {
+#pragma unroll 1
+          for (int nb = 0; nb < tile.nvalid; nb += GM_EPI_ROWS) {
+            const int nrows = min(GM_EPI_ROWS, tile.nvalid - nb);
+            // ---- phase 1: tensor memory -> registers -> epilogue arithmetic -> staged tile
+            if (PAIR || !SWIGLU) {
+              for (int n0 = nb; n0 < nb + nrows; n0 += 8) {
+                uint32_t v0[8], v1[8];
+                if (alive) {
+                  tmem_ld_x8(taddr + acc * BN + n0, v0);
+                  if (SWIGLU) tmem_ld_x8(taddr + BN + n0, v1);
+                  tmem_ld_wait();
+                }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
-          }
-          named_barrier_sync(2, GM_EPI_WARPS * 32);
-          if (q < 2 && alive) {
+                for (int j = 0; j < 8; ++j) {
+                  if (alive && n0 + j < tile.nvalid) {
+                    const float f0 = __uint_as_float(v0[j]);
+                    T o;
+                    if (SWIGLU) o = epilogue_swiglu<T>(f0, __uint_as_float(v1[j]));
+                    else if (SCALE) o = epilogue_scale<T>(f0, scale[tile.row0 + n0 + j]);
+                    else o = Elem<T>::from_f(f0);
+                    *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + wrow * 2) = o;
+                  }
+                }
+              }
+            } else {
+              // one accumulator: lanes 0-63 hold the gate rows, lanes 64-127 the up rows of the
+              // same 64 output columns. Warps 2,3 pass their values to warps 0,1 through shared
+              // memory (double-buffered by chunk, one barrier per chunk).
+              const int j64 = wrow & 63;
+              for (int n0 = nb; n0 < nb + nrows; n0 += 8, ++chunk_no) {
+                uint32_t v[8];
+                if (alive) {
+                  tmem_ld_x8(taddr + n0, v);
+                  tmem_ld_wait();
+                }
+                float* slot = s_xch[chunk_no & 1][j64];
+                if (q >= 2 && alive) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int row = tile.row0 + n0 + j;
-              if (n0 + j < tile.nvalid && col < Nout)
-                Cg[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
+                  for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
+                }
+                named_barrier_sync(2, GM_EPI_WARPS * 32);
+                if (q < 2 && alive) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (n0 + j < tile.nvalid)
+                      *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + j64 * 2) =
+                          epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
+                }
+              }
             }
+            named_barrier_sync(3, GM_EPI_WARPS * 32);
+            // ---- phase 2: staged tile -> memory, 16 bytes per thread, whole row segments
+            const int col = tile.cb * COLS + acc * GM_BM + (et % TPR) * 8;
+            if (alive && col < Nout) {
+              for (int r = et / TPR; r < nrows; r += GM_EPI_WARPS * 32 / TPR)
+                *reinterpret_cast<uint4*>(Cg + (size_t)(tile.row0 + nb + r) * Nout + col) =
+                    *reinterpret_cast<const uint4*>(out_tile + r * ORB + (et % TPR) * 16);
+            }
+            named_barrier_sync(3, GM_EPI_WARPS * 32);
           }
         }
       }
@@ -546,7 +629,8 @@ int grouped_umma(bool pair, const char* name, const GroupedArgs& a, int rows, in
   SY_REQUIRE(a.dtype == SY_DTYPE_F16 || a.dtype == SY_DTYPE_BF16, "%s: dtype must be f16 or bf16", name);
   if (rows == 0) return SY_OK;
   SY_REQUIRE(a.A && a.B && a.begins && a.ends && (a.C || a.c_table), "%s: null pointer", name);
-  SY_REQUIRE(((uintptr_t)a.A % 16 == 0) && ((uintptr_t)a.B % 16 == 0), "%s: A and B must be 16-byte aligned", name);
+  SY_REQUIRE(((uintptr_t)a.A % 16 == 0) && ((uintptr_t)a.B % 16 == 0) && ((uintptr_t)a.C % 16 == 0),
+             "%s: A, B and C must be 16-byte aligned", name);
   if (a.dtype == SY_DTYPE_F16) return pair ? dispatch_gemm<__half, true>(a, swiglu) : dispatch_gemm<__half, false>(a, swiglu);
   return pair ? dispatch_gemm<__nv_bfloat16, true>(a, swiglu) : dispatch_gemm<__nv_bfloat16, false>(a, swiglu);
 }
