@@ -143,10 +143,13 @@ int sy_enable_peer_access(int device, int peer, int* enabled_out);
  * See csrc/ep.cu for the protocol. All pointer tables are HOST arrays of device pointers. */
 
 /* grouped_segments — sy_grouped_gemv (compute_shape = 0) or sy_grouped_gemm (1) over explicit
- * row groups: group g is rows [begins[g], ends[g]) of A (no gather) and uses the weights
- * B[g / groups_per_expert]. begins/ends are device arrays of n_groups ints. If c_table is not
- * NULL, row begins[g] + i of group g is stored at ((T*)c_table[g]) + i*n_out instead of in C (the
- * destination may be a peer GPU's memory). rows_bound: any upper bound of the rows (0 = no-op). */
+ * row ranges. Range g is rows [begins[g], ends[g]) of A (no gather); expert e (weights B[e])
+ * owns the groups_per_expert consecutive ranges starting at e*groups_per_expert, and its tiles
+ * run over their concatenation, so the expert's weights are read once for all of them.
+ * begins/ends are device arrays of n_groups ints. Results are stored at the same row index in C,
+ * or, if c_table is not NULL, row begins[g] + i of range g goes to ((T*)c_table[g]) + i*n_out
+ * (the destination may be a peer GPU's memory). rows_bound: any upper bound of the rows
+ * (0 = no-op). */
 int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, const int32_t* ends, int n_groups,
                         int groups_per_expert, int rows_bound, int n_out, int k_dim, int swiglu, const void* scale,
                         void* C, const uint64_t* c_table, int dtype, int compute_shape, void* stream);

@@ -99,22 +99,32 @@ __device__ long long g_prof[256][16];
 #define SY_PROF_STORE(slot, v)
 #endif
 
-// Tile t of the device-side numbering; `cursor` walks the experts monotonically.
-// A group is a set of consecutive rows [begin, end) that goes through one expert's weights:
-// an expert's slice of the sorted batch, or, in an expert-parallel mailbox, one sender's rows
-// for one local expert.
+// Rows come in ranges [begin, end). Normally an expert has one range: its slice of the sorted
+// batch. In an expert-parallel mailbox an expert has `ranges_per_expert` of them, one per
+// sender, and its tile rows are their concatenation: the expert's weights are streamed once for
+// all senders. Tile t of the device-side numbering belongs to expert e (weights B[e]) and covers
+// rows [r0, r0 + nvalid) of that concatenation; `cursor` walks the experts monotonically.
 template <int BN>
-__device__ __forceinline__ Tile locate_tile(int t, int& cursor, const int* tile_start, const int* begin,
-                                            const int* end) {
+__device__ __forceinline__ Tile locate_tile(int t, int& cursor, const int* tile_start, const int* expert_rows) {
   while (tile_start[cursor + 1] <= t) ++cursor;
   const int e = cursor, local = t - tile_start[e];
-  const int n = end[e] - begin[e], row_tiles = (n + BN - 1) / BN;
+  const int n = expert_rows[e], row_tiles = (n + BN - 1) / BN;
   Tile tile;
   tile.e = e;
   tile.cb = local / row_tiles;
-  tile.row0 = begin[e] + (local % row_tiles) * BN;
-  tile.nvalid = min(BN, end[e] - tile.row0);
+  tile.row0 = (local % row_tiles) * BN;
+  tile.nvalid = min(BN, n - tile.row0);
   return tile;
+}
+
+// Row r of expert e's concatenated ranges: the range it falls in (g) and its row in A / C space.
+__device__ __forceinline__ int map_row(int e, int r, int ranges_per_expert, const int* begin, const int* end, int& g) {
+  g = e * ranges_per_expert;
+  for (int len = end[g] - begin[g]; r >= len; len = end[g] - begin[g]) {
+    r -= len;
+    ++g;
+  }
+  return begin[g] + r;
 }
 
 template <typename T, bool SWIGLU, bool SCALE, bool PAIR>
@@ -133,8 +143,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
-  __shared__ int s_begin[GM_MAX_E];
+  __shared__ int s_begin[GM_MAX_E];       // row ranges
   __shared__ int s_end[GM_MAX_E];
+  __shared__ int s_rows[GM_MAX_E];        // rows per expert (all its ranges)
+  __shared__ int s_map_row[2][GM_BM];     // per accumulator buffer: the tile's rows in A / C space
+  __shared__ int s_map_grp[2][GM_BM];     // ... and the range each row belongs to
   __shared__ int s_tile_start[GM_MAX_E + 2];
   __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (!PAIR SwiGLU)
 
@@ -165,23 +178,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     prefetch_tensormap(&w_map);
   }
   __syncthreads();
-  if (warp == 0) {  // exclusive prefix of tiles per expert
+  const int EL = E / group_div;  // experts; E counts row ranges
+  if (warp == 0) {  // rows per expert and the exclusive prefix of tiles per expert
     int carry = 0;
-    for (int base = 0; base < E; base += 32) {
+    for (int base = 0; base < EL; base += 32) {
       int e = base + lane;
-      int n = e < E ? s_end[e] - s_begin[e] : 0;
+      int n = 0;
+      if (e < EL)
+        for (int g = e * group_div; g < (e + 1) * group_div; ++g) n += s_end[g] - s_begin[g];
+      if (e < EL) s_rows[e] = n;
       int tiles = ((n + BN - 1) / BN) * col_blocks, inc = tiles;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         int y = __shfl_up_sync(0xffffffffu, inc, o);
         if (lane >= o) inc += y;
       }
-      if (e < E) s_tile_start[e] = carry + inc - tiles;
+      if (e < EL) s_tile_start[e] = carry + inc - tiles;
       carry += __shfl_sync(0xffffffffu, inc, 31);
     }
     if (lane == 0) {
-      s_tile_start[E] = carry;
-      s_tile_start[E + 1] = 0x7fffffff;  // sentinel: the cursor never walks past E
+      s_tile_start[EL] = carry;
+      s_tile_start[EL + 1] = 0x7fffffff;  // sentinel: the cursor never walks past the last expert
     }
   }
   if (warp == 1) {
@@ -192,7 +209,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = s_tmem;
-  const int total_tiles = s_tile_start[E];
+  const int total_tiles = s_tile_start[EL];
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -202,8 +219,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       SY_PROF_DECL(w_empty);
       SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
-        const int y0 = (tile.e / group_div) * Nfull + tile.cb * COLS;  // group g uses weights g / group_div
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_rows);
+        const int y0 = tile.e * Nfull + tile.cb * COLS;
         const int y1 = SWIGLU ? y0 + Nout : y0 + S::BOX_ROWS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES, use = it / STAGES;
@@ -241,7 +258,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       SY_PROF_DECL(w_acc);
       SY_PROF_BEGIN(t_role);
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_no) {
-        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
+        const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_rows);
         const int buf = tile_no & 1, use_t = tile_no >> 1;
         if (use_t > 0) {
           SY_PROF_BEGIN(t_w);
@@ -306,7 +323,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     SY_PROF_DECL(w_rows);
     SY_PROF_BEGIN(t_role);
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
-      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_rows);
       const T* src[GI];
       SY_PROF_BEGIN(t_r);
 #pragma unroll
@@ -314,7 +331,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
         const int r = rsub + ROWS_PER_PASS * i;
         src[i] = nullptr;
         if (r < tile.nvalid) {
-          const int row = a_rows ? a_rows[tile.row0 + r] : tile.row0 + r;
+          int g;
+          const int at = map_row(tile.e, tile.row0 + r, group_div, s_begin, s_end, g);
+          const int row = a_rows ? a_rows[at] : at;
           src[i] = A + (size_t)row * K + c * 8;
         }
       }
@@ -369,7 +388,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     SY_PROF_DECL(w_accf);
     SY_PROF_BEGIN(t_role);
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
-      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_begin, s_end);
+      const Tile tile = locate_tile<BN>(t, cursor, s_tile_start, s_rows);
       const int buf = tile_no & 1, use_t = tile_no >> 1;
       SY_PROF_BEGIN(t_w);
       if (alive && !mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
@@ -380,9 +399,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       tc_fence_after_sync();
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * S::BUF_COLS;
       const int wrow = q * 32 + lane;
-      // where this group's rows go: C, or (expert-parallel return) wherever c_table says the
-      // group's first row lands, possibly in a peer GPU's memory
-      T* __restrict__ Cg = c_table ? reinterpret_cast<T*>(c_table[tile.e]) - (size_t)s_begin[tile.e] * Nout : C;
+      const int et = threadIdx.x - (2 + GM_GATHER_WARPS) * 32;  // 0..127 among the epilogue threads
+      // the tile's rows in A / C space (and the range of each), once per tile for all four warps
+      int* map_row_s = s_map_row[buf];
+      int* map_grp_s = s_map_grp[buf];
+      if (et < tile.nvalid) {
+        int g;
+        map_row_s[et] = map_row(tile.e, tile.row0 + et, group_div, s_begin, s_end, g);
+        map_grp_s[et] = g;
+      }
+      named_barrier_sync(3, GM_EPI_WARPS * 32);
       if (!c_table) {
         // Local destination: every thread stores its own column's values directly (2 bytes per
         // store, a warp covers 64 contiguous bytes of a row); L2 merges them, and the epilogue
@@ -397,8 +423,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const int row = tile.row0 + n0 + j;
               if (n0 + j < tile.nvalid) {
+                const int row = map_row_s[n0 + j];
                 const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
                 if (SWIGLU) {
                   if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
@@ -433,9 +459,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
             if (q < 2 && alive) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const int row = tile.row0 + n0 + j;
                 if (n0 + j < tile.nvalid && col < Nout)
-                  C[(size_t)row * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
+                  C[(size_t)map_row_s[n0 + j] * Nout + col] = epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
               }
             }
           }
@@ -449,7 +474,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
         constexpr int ORB = OC * 2;                               // bytes per staged row
         constexpr int TPR = ORB / 16;                             // threads per row when copying out
         constexpr int STORE_ACCS = (PAIR && !SWIGLU) ? 2 : 1;
-        const int et = threadIdx.x - (2 + GM_GATHER_WARPS) * 32;  // 0..127 among the epilogue threads
 #pragma unroll 1
         for (int acc = 0; acc < STORE_ACCS; ++acc) {
 #pragma unroll 1
@@ -470,7 +494,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
                     const float f0 = __uint_as_float(v0[j]);
                     T o;
                     if (SWIGLU) o = epilogue_swiglu<T>(f0, __uint_as_float(v1[j]));
-                    else if (SCALE) o = epilogue_scale<T>(f0, scale[tile.row0 + n0 + j]);
+                    else if (SCALE) o = epilogue_scale<T>(f0, scale[map_row_s[n0 + j]]);
                     else o = Elem<T>::from_f(f0);
                     *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + wrow * 2) = o;
                   }
@@ -506,9 +530,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
             // ---- phase 2: staged tile -> memory, 16 bytes per thread, whole row segments
             const int col = tile.cb * COLS + acc * GM_BM + (et % TPR) * 8;
             if (alive && col < Nout) {
-              for (int r = et / TPR; r < nrows; r += GM_EPI_WARPS * 32 / TPR)
-                *reinterpret_cast<uint4*>(Cg + (size_t)(tile.row0 + nb + r) * Nout + col) =
-                    *reinterpret_cast<const uint4*>(out_tile + r * ORB + (et % TPR) * 16);
+              for (int r = et / TPR; r < nrows; r += GM_EPI_WARPS * 32 / TPR) {
+                // c_table[g] is where row s_begin[g] of range g lands
+                const int g = map_grp_s[nb + r];
+                T* dst = reinterpret_cast<T*>(c_table[g]) + (size_t)(map_row_s[nb + r] - s_begin[g]) * Nout + col;
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(out_tile + r * ORB + (et % TPR) * 16);
+              }
             }
             named_barrier_sync(3, GM_EPI_WARPS * 32);
           }
@@ -576,8 +603,8 @@ struct GroupedArgs {
   const void* B;
   const int32_t* begins;   // [groups] first row of each group
   const int32_t* ends;     // [groups] one past its last row
-  int groups;              // number of groups (an expert's slice; or local expert x sender)
-  int group_div;           // group g uses weights B[g / group_div]
+  int groups;              // number of row ranges (experts x ranges per expert)
+  int group_div;           // ranges per expert: ranges [e*group_div, (e+1)*group_div) are expert e's rows
   int n_out, k_dim;
   const void* scale;
   void* C;
