@@ -189,3 +189,78 @@ def run(args):
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
+# The other benchmark configurations (reported in DESIGN.md; the driver's bench line is the
+# decode sweep above): config 3 = 256 tokens per GPU, fp16, Zipf-skewed routing;
+# config 4 = prefill, 1024 / 4096 / 8192 tokens per GPU, bf16, same skew.
+def run_config(args):
+    from . import kernels, synthetic
+    import bench
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.config == "ep256":
+        dtype, sizes, mode = torch.float16, (256,), "gemm" if world == 1 else "gemv"
+    else:
+        dtype, sizes, mode = torch.bfloat16, (1024, 4096, 8192), "gemm"
+    per = E // world
+    n_sets = 3
+    layers = [rank_weights(dev, dtype, 100 + l, rank * per, (rank + 1) * per) for l in range(n_sets)]
+    bias = synthetic.zipf_bias()
+    out = []
+    for T in sizes:
+        h = synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T)
+        if world > 1:
+            from .ep_dist import DistributedExpertParallel
+            # with 64/R rows per expert per token-batch the streaming shape holds up to 64 rows a tile
+            m = "gemv" if T * world * TOPK * 4 // E <= 64 else "gemm"
+            ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode=m, device=dev,
+                                           logit_bias=bias)
+            run = lambda l: ep.layer(h, *layers[l])
+            mode_used = m
+        else:
+            b = bias.to(dev).to(dtype)
+
+            def run(l):
+                router, gu, dn = layers[l]
+                idx, w = kernels.ext().route((torch.nn.functional.linear(h, router) + b).contiguous(), TOPK, False)
+                return kernels.experts(h, idx, w, gu, dn, mode)
+            mode_used = mode
+        stream = torch.cuda.Stream(dev)
+        with torch.cuda.stream(stream):
+            for i in range(max(args.warmup, 3)):
+                run(i % n_sets)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for i in range(args.steps):
+                run(i % n_sets)
+            t1.record(stream)
+            torch.cuda.synchronize()
+        ms = torch.tensor([t0.elapsed_time(t1) / args.steps], dtype=torch.float64, device=dev)
+        # routing skew actually achieved (rank 0's tokens)
+        idx, _ = kernels.ext().route((torch.nn.functional.linear(h, layers[0][0]) + bias.to(dev).to(dtype)).contiguous(),
+                                     TOPK, False)
+        skew = synthetic.busiest_over_mean(idx)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            ep.close()
+        ms = float(ms)
+        rows = T * world * TOPK
+        out.append({"tokens_per_gpu": T, "ms_per_layer": ms, "tokens_per_s": T * world / (ms / 1e3),
+                    "tflops": rows * 12582912 / (ms / 1e3) / 1e12, "tflops_per_gpu": rows * 12582912 / (ms / 1e3) / 1e12 / world,
+                    "mode": mode_used, "busiest_over_mean": skew})
+    if rank == 0:
+        print(json.dumps({"config": args.config, "n_gpus": world, "dtype": str(dtype).replace("torch.", ""),
+                          "steps": args.steps, "timing": "CUDA events, eager launches, max over ranks",
+                          "results": out, "device_status": kernels.ext().device_status(dev)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
