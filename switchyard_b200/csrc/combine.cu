@@ -17,6 +17,8 @@ combine_kernel(const T* __restrict__ y, const int* __restrict__ pos_of, const in
                T* __restrict__ out) {
   __shared__ int s_row[COMBINE_MAX_K];
   const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();  // y comes from the down projection before this kernel
   if (threadIdx.x < k) {
     // rank of this slot among the token's k choices by (expert id, slot)
     int e = idx[(size_t)t * k + threadIdx.x], rank = 0;
@@ -62,10 +64,9 @@ extern "C" int sy_combine(const void* y, const int32_t* pos_of, const int32_t* i
   SY_REQUIRE(((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0), "combine: y and out must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == SY_DTYPE_F16)
-    combine_kernel<__half><<<n_tokens, COMBINE_THREADS, 0, s>>>(static_cast<const __half*>(y), pos_of, idx, top_k,
-                                                                hidden, static_cast<__half*>(out));
-  else
-    combine_kernel<__nv_bfloat16><<<n_tokens, COMBINE_THREADS, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(y), pos_of, idx, top_k, hidden, static_cast<__nv_bfloat16*>(out));
-  return check_cuda(cudaGetLastError(), "combine launch");
+    return launch_kernel(combine_kernel<__half>, n_tokens, COMBINE_THREADS, 0, s, "combine launch",
+                         static_cast<const __half*>(y), pos_of, idx, top_k, hidden, static_cast<__half*>(out));
+  return launch_kernel(combine_kernel<__nv_bfloat16>, n_tokens, COMBINE_THREADS, 0, s, "combine launch",
+                       static_cast<const __nv_bfloat16*>(y), pos_of, idx, top_k, hidden,
+                       static_cast<__nv_bfloat16*>(out));
 }

@@ -33,6 +33,35 @@ int* device_status_word();               // device address of this device's kern
 
 constexpr int MAX_DEVICES = 64;
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// The layer is a chain of short kernels. Each is launched with the programmatic-serialization
+// attribute, lets its successor start as soon as it is resident (pdl_launch_dependents), does
+// whatever does not touch its inputs (barrier and tensor-memory set-up), and only then waits
+// for its predecessors to finish (pdl_wait). Launch latency and prologues overlap the previous
+// kernel's tail; results are unchanged. SY_NO_PDL=1 in the environment turns it off.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const char* what,
+                  Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...), what);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 // ---- 16-bit element helpers ---------------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<__half> {

@@ -160,11 +160,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
   const int Nfull = SWIGLU ? 2 * Nout : Nout;
   const int k_blocks = (K + S::BK - 1) / S::BK;
 
-  for (int i = threadIdx.x; i < E; i += GM_THREADS) {
-    const int b = begins[i], e = ends[i];
-    s_begin[i] = b;
-    s_end[i] = e > b ? e : b;
-  }
+  // Set-up that touches none of the kernel's inputs comes first, so that under programmatic
+  // dependent launch it overlaps the tail of the previous kernel.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1 + GM_GATHER_WARPS);
@@ -176,6 +174,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
     }
     fence_barrier_init();
     prefetch_tensormap(&w_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem, S::TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_wait();  // row ranges, activations, scale: all written by earlier kernels
+  for (int i = threadIdx.x; i < E; i += GM_THREADS) {
+    const int b = begins[i], e = ends[i];
+    s_begin[i] = b;
+    s_end[i] = e > b ? e : b;
   }
   __syncthreads();
   const int EL = E / group_div;  // experts; E counts row ranges
@@ -200,10 +208,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap w_map, const T* __restrict_
       s_tile_start[EL] = carry;
       s_tile_start[EL + 1] = 0x7fffffff;  // sentinel: the cursor never walks past the last expert
     }
-  }
-  if (warp == 1) {
-    tmem_alloc(&s_tmem, S::TMEM_COLS);
-    tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -632,10 +636,9 @@ static int launch_gemm(const GroupedArgs& a) {
     SY_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
     configured[dev].store(1, std::memory_order_release);
   }
-  kern<<<sms, GM_THREADS, GM_SMEM, a.stream>>>(map, static_cast<const T*>(a.A), a.a_rows, a.begins, a.ends, a.groups,
-                                               a.group_div, a.n_out, a.k_dim, static_cast<const T*>(a.scale),
-                                               static_cast<T*>(a.C), a.c_table, status);
-  return check_cuda(cudaGetLastError(), "grouped tcgen05 launch");
+  return launch_kernel(kern, sms, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", map,
+                       static_cast<const T*>(a.A), a.a_rows, a.begins, a.ends, a.groups, a.group_div, a.n_out, a.k_dim,
+                       static_cast<const T*>(a.scale), static_cast<T*>(a.C), a.c_table, status);
 }
 
 template <typename T, bool PAIR>

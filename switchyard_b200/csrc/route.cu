@@ -15,6 +15,8 @@ template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int norm, int* __restrict__ idx,
              T* __restrict__ w) {
+  pdl_launch_dependents();
+  pdl_wait();  // the logits come from the kernel before this one
   const int lane = threadIdx.x & 31;
   const int token = (blockIdx.x * ROUTE_THREADS + threadIdx.x) >> 5;
   if (token >= n_tokens) return;
@@ -86,13 +88,9 @@ static int launch_route(const void* logits, int n_tokens, int E, int k, int norm
   int blocks = (n_tokens * 32 + ROUTE_THREADS - 1) / ROUTE_THREADS;
   const T* l = static_cast<const T*>(logits);
   T* wp = static_cast<T*>(w);
-  if (E <= 32)
-    route_kernel<T, 1><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
-  else if (E <= 64)
-    route_kernel<T, 2><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
-  else
-    route_kernel<T, 4><<<blocks, ROUTE_THREADS, 0, stream>>>(l, n_tokens, E, k, norm, idx, wp);
-  return check_cuda(cudaGetLastError(), "route launch");
+  if (E <= 32) return launch_kernel(route_kernel<T, 1>, blocks, ROUTE_THREADS, 0, stream, "route launch", l, n_tokens, E, k, norm, idx, wp);
+  if (E <= 64) return launch_kernel(route_kernel<T, 2>, blocks, ROUTE_THREADS, 0, stream, "route launch", l, n_tokens, E, k, norm, idx, wp);
+  return launch_kernel(route_kernel<T, 4>, blocks, ROUTE_THREADS, 0, stream, "route launch", l, n_tokens, E, k, norm, idx, wp);
 }
 
 }  // namespace sy

@@ -2,6 +2,7 @@
 // address of the kernel status word), version and status entry points.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -25,6 +26,14 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(t_error, sizeof(t_error), fmt, ap);
   va_end(ap);
   return code;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("SY_NO_PDL");
+    return !(v && v[0] == '1');
+  }();
+  return on;
 }
 
 int check_cuda(cudaError_t e, const char* what) {

@@ -123,6 +123,8 @@ sort_single_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, 
   int* total = wcount + SORT_WARPS * E;   // [E]
   int* off = total + E;                   // [E + 1]
   const int per_warp = per_block / SORT_WARPS;
+  pdl_launch_dependents();
+  pdl_wait();  // idx and w come from the routing kernel
   count_chunk(idx, m, 0, per_warp, E, wcount);
   for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
     int s = 0;
@@ -212,8 +214,8 @@ static int launch_sort(const int32_t* idx, const void* w, int m, int k, int E, i
   const T* wp = static_cast<const T*>(w);
   T* ws = static_cast<T*>(wsorted);
   if (s.blocks == 1) {
-    sort_single_kernel<T><<<1, SORT_THREADS, smem, stream>>>(idx, wp, m, k, E, s.per_block, counts, offsets, token,
-                                                             ws, pos_of, status);
+    return launch_kernel(sort_single_kernel<T>, 1, SORT_THREADS, smem, stream, "sort launch", idx, wp, m, k, E,
+                         s.per_block, counts, offsets, token, ws, pos_of, status);
   } else {
     int* table = static_cast<int*>(scratch);
     sort_count_kernel<<<s.blocks, SORT_THREADS, (size_t)SORT_WARPS * E * sizeof(int), stream>>>(idx, m, E, s.per_block,
