@@ -113,6 +113,28 @@ int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const i
                     int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                     int dtype, void* stream);
 
+/* expert_ffn — the whole expert FFN of a layer in ONE launch: gate/up projection with SwiGLU
+ * into `act`, then the down projection scaled by the router weights into `y`, i.e. what the
+ * reference does with two grouped_gemv / grouped_gemm calls (switchyard/kernels.py:56-63). A down
+ * tile of an expert starts as soon as that expert's gate/up tiles have been stored (a counter
+ * per expert in `scratch`, bounded wait), so the second projection fills the SMs that the first
+ * one's last tiles leave idle, and there is no launch gap between them. Arithmetic per row is
+ * that of the two separate calls, bit for bit.
+ * Rows come as ranges like sy_grouped_segments: range g = rows [begins[g], ends[g]); expert e owns
+ * ranges [e*ranges_per_expert, (e+1)*ranges_per_expert). For the plain single-GPU layer pass
+ * begins = offsets, ends = offsets + 1, n_ranges = experts, ranges_per_expert = 1.
+ * x 16-bit [*, hidden] (row i of a range is x[a_rows ? a_rows[i] : i]); gate_up [experts, 2*inter,
+ * hidden]; down [experts, hidden, inter]; wsorted 16-bit router weight per row; act 16-bit
+ * [rows_bound, inter] scratch; y 16-bit [rows_bound, hidden], or y_table as c_table above.
+ * scratch: sy_expert_ffn_scratch_bytes(experts) bytes, zero before the first call; the kernel
+ * leaves it zero again. Calls that share one scratch must not overlap (one per stream).
+ * compute_shape: 0 = streaming shape (decode), 1 = compute shape (prefill). */
+size_t sy_expert_ffn_scratch_bytes(int n_experts);
+int sy_expert_ffn(const void* x, const int32_t* a_rows, const void* gate_up, const void* down, const int32_t* begins,
+                  const int32_t* ends, int n_ranges, int ranges_per_expert, int rows_bound, int hidden, int inter,
+                  const void* wsorted, void* act, void* y, const uint64_t* y_table, int32_t* scratch, int dtype,
+                  int compute_shape, void* stream);
+
 /* combine — replaces `combine` (moe_kernels.cu:435-444, kernel l.417-433).
  * out[t, :] = round16( sum_j float(y[pos_of[t*top_k + order_j], :]) ), the token's top_k rows
  * added in ascending expert id (ties in slot order), float32 accumulation, one rounding.

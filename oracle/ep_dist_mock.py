@@ -150,6 +150,14 @@ class _Lib:
                     out[r] = acc.to(dt)[0]
         return 0
 
+    def sy_expert_ffn(self, x, a_rows, gate_up, down, begins, ends, n_ranges, per_expert, rows_bound, hidden, inter,
+                      wsorted, act, y, y_table, scratch, dtype, compute_shape, stream):
+        assert not _addr(a_rows)
+        rc = self.sy_grouped_segments(x, gate_up, begins, ends, n_ranges, per_expert, rows_bound, inter, hidden, 1, None,
+                                      act, None, dtype, compute_shape, stream)
+        return rc or self.sy_grouped_segments(act, down, begins, ends, n_ranges, per_expert, rows_bound, hidden, inter, 0,
+                                              wsorted, y, y_table, dtype, compute_shape, stream)
+
     def sy_ep_signal(self, flag_dst, R, epoch_counter, stream):
         epoch = int(_view(epoch_counter, 1, np.int32)[0])
         for s in range(R):

@@ -30,6 +30,9 @@ SYMBOLS = {
                                 c_void_p, c_int, c_void_p]),
     "sy_grouped_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p]),
+    "sy_expert_ffn_scratch_bytes": (c_size_t, [c_int]),
+    "sy_expert_ffn": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "sy_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "sy_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "sy_copy_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),

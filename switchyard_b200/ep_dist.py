@@ -3,13 +3,13 @@ device-driven transport (csrc/ep.cu).
 
 `ep.ExpertParallel` mirrors the reference: one process drives all GPUs with a thread per rank,
 events between streams and one host read per layer. `DistributedExpertParallel` is the form for
-one process per GPU: every rank maps every other rank's window (CUDA IPC), a layer is ten
+one process per GPU: every rank maps every other rank's window (CUDA IPC), a layer is nine
 launches on the rank's stream, and the host never reads anything back:
 
     router GEMM, route, sort                      (local tokens, global expert ids)
     ep_dispatch                                   rows -> owners' mailboxes, arrival flags
     ep_wait_build                                 wait for all senders, build row groups
-    grouped kernel x2                             experts; results stored straight into the senders' y
+    expert_ffn                                    both projections; results stored straight into the senders' y
     ep_signal                                     return flags
     ep_wait, combine                              wait for all owners, sum in expert order
 
@@ -146,6 +146,7 @@ class DistributedExpertParallel:
         self.groups = self.backend.zeros(2 * G, torch.int32)
         self.c_table = self.backend.zeros(G, torch.int64)
         self.act = self.backend.empty((self.R * cap, inter), dtype)
+        self.ffn_scratch = self.backend.zeros(self.per + 1, torch.int32)
         dist.barrier(group=group)  # every window is mapped everywhere before the first layer
 
     def layer(self, h, router, gate_up, down):
@@ -174,11 +175,9 @@ class DistributedExpertParallel:
             begins, ends = self.groups.data_ptr(), self.groups.data_ptr() + 4 * G
             _lib.check(lib.sy_ep_wait_build(self.p_arrive, self.p_meta, per, R, cap, self.y_dst, H * self.elem, epoch,
                                             begins, ends, self.c_table.data_ptr(), stream), "ep_wait_build")
-            _lib.check(lib.sy_grouped_segments(self.p_x, gate_up.data_ptr(), begins, ends, G, R, R * cap, self.I, H, 1,
-                                               None, self.act.data_ptr(), None, code, shape, stream), "grouped_segments")
-            _lib.check(lib.sy_grouped_segments(self.act.data_ptr(), down.data_ptr(), begins, ends, G, R, R * cap, H,
-                                               self.I, 0, self.p_w, None, self.c_table.data_ptr(), code, shape, stream),
-                       "grouped_segments")
+            _lib.check(lib.sy_expert_ffn(self.p_x, None, gate_up.data_ptr(), down.data_ptr(), begins, ends, G, R, R * cap,
+                                         H, self.I, self.p_w, self.act.data_ptr(), None, self.c_table.data_ptr(),
+                                         self.ffn_scratch.data_ptr(), code, shape, stream), "expert_ffn")
             _lib.check(lib.sy_ep_signal(self.ret_dst, R, epoch, stream), "ep_signal")
             _lib.check(lib.sy_ep_wait(self.p_ret, R, epoch, stream), "ep_wait")
         return ext.combine(self.y, pos_of, idx, N)

@@ -73,6 +73,41 @@ class Ext:
 
     def __init__(self):
         self.lib = _lib.load()
+        self._ffn_scratch = {}  # (device, stream) -> zeroed counters of the fused FFN kernel
+
+    def ffn_scratch(self, device, stream, experts):
+        """The fused FFN kernel's per-expert counters: zero-initialised once, left zero by every
+        launch, and private to one stream (launches sharing them must not overlap)."""
+        key = (device.index, stream, experts)
+        t = self._ffn_scratch.get(key)
+        if t is None:
+            t = torch.zeros(experts + 1, dtype=torch.int32, device=device)
+            self._ffn_scratch[key] = t
+        return t
+
+    def expert_ffn(self, x, a_rows, gate_up, down, offsets, rows, wsorted, compute_shape):
+        """Both projections of the expert FFN in one launch (sy_expert_ffn): returns y [rows, H]."""
+        _check(x, "x"), _check(gate_up, "gate_up"), _check(down, "down"), _check(offsets, "offsets")
+        _check(wsorted, "wsorted")
+        code = _dtype_code(x, "expert_ffn")
+        E, I2, H = gate_up.shape
+        if down.shape != (E, H, I2 // 2) or x.shape[1] != H or gate_up.dtype != x.dtype or down.dtype != x.dtype:
+            raise RuntimeError("expert_ffn: shapes or dtypes do not match")
+        if offsets.dtype != torch.int32 or offsets.numel() != E + 1:
+            raise RuntimeError("expert_ffn: offsets must be int32 [E+1]")
+        if a_rows is not None:
+            _check(a_rows, "a_rows")
+        y = torch.empty(rows, H, dtype=x.dtype, device=x.device)
+        if rows == 0:
+            return y
+        act = torch.empty(rows, I2 // 2, dtype=x.dtype, device=x.device)
+        with _Device(x.device) as stream:
+            scratch = self.ffn_scratch(x.device, stream, E)
+            _lib.check(self.lib.sy_expert_ffn(_ptr(x), _ptr(a_rows), _ptr(gate_up), _ptr(down), _ptr(offsets),
+                                              offsets.data_ptr() + 4, E, 1, int(rows), H, I2 // 2, _ptr(wsorted),
+                                              _ptr(act), _ptr(y), None, _ptr(scratch), code, int(compute_shape), stream),
+                       "expert_ffn")
+        return y
 
     def route(self, logits, k, norm):
         _check(logits, "logits")
@@ -228,12 +263,12 @@ def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_cou
     if rows == 0:
         return torch.empty(0, down.shape[1], dtype=x.dtype, device=x.device)
     x = x.contiguous()
+    # one launch for both projections (bit-identical to grouped_gemv / grouped_gemm called twice,
+    # which remain available on ext() as in the reference)
     if mode == "gemv":
-        act = E.grouped_gemv(x, a_rows, gate_up, offsets, rows, True, None)
-        return E.grouped_gemv(act, None, down, offsets, rows, False, wsorted)
+        return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 0)
     if mode in ("gemm", "cublas"):
-        act = E.grouped_gemm(x, a_rows, gate_up, offsets, None, 0, rows, True, None)
-        return E.grouped_gemm(act, None, down, offsets, None, 0, rows, False, wsorted)
+        return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 1)
     raise RuntimeError(f"ffn: unknown mode {mode!r}")
 
 

@@ -208,6 +208,30 @@ def test_a_rows_bits_do_not_depend_on_its_group(K, mode):
         assert torch.equal(y.cpu(), full.cpu()[rows])
 
 
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+@pytest.mark.parametrize("N,skew", [(1, 0.0), (64, 0.0), (97, 2.0), (700, 2.0)])
+def test_fused_ffn_equals_the_two_grouped_calls(K, mode, N, skew):
+    """ffn() runs both projections in one launch; bit for bit the same as grouped_gemv /
+    grouped_gemm called twice (the reference's structure), several times in a row (the kernel's
+    per-expert counters must come back to zero)."""
+    h, router, gu, dn = cases.layer_inputs(N, skew=skew)
+    ridx, rw = mo.route_reference(h, router, 8, False)
+    counts, offsets, token, wsorted, pos_of = mo.sort_by_expert(ridx.int(), rw, 64)
+    hd, gud, dnd = h.to(DEV), gu.to(DEV), dn.to(DEV)
+    tok, off, ws = token.to(DEV), offsets.to(DEV), wsorted.to(DEV)
+    M = token.numel()
+    E = K.ext()
+    if mode == "gemv":
+        act = E.grouped_gemv(hd, tok, gud, off, M, True, None)
+        want = E.grouped_gemv(act, None, dnd, off, M, False, ws)
+    else:
+        act = E.grouped_gemm(hd, tok, gud, off, None, 0, M, True, None)
+        want = E.grouped_gemm(act, None, dnd, off, None, 0, M, False, ws)
+    for _ in range(3):
+        got = K.ffn(hd, tok, off, counts.to(DEV), ws, gud, dnd, M, mode)
+        assert torch.equal(got, want)
+
+
 # ------------------------------------------------------------------------------ OLMoE shapes
 @pytest.fixture(scope="module")
 def olmoe():
