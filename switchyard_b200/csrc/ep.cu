@@ -77,6 +77,8 @@ ep_dispatch_kernel(const uint4* __restrict__ h, const int* __restrict__ token, c
                    DispatchTargets tg, int* done_counter, int* epoch_counter, int* status) {
   __shared__ int s_seg[EP_MAX_RANKS + 1];
   __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();  // offsets, token, wsorted come from the sort before this kernel
   if (threadIdx.x <= R) s_seg[threadIdx.x] = offsets[threadIdx.x * per];
   __syncthreads();
   if (blockIdx.x == 0) {
@@ -133,6 +135,8 @@ ep_wait_build_kernel(const int* arrive_flags, const int* meta, int per, int R, i
                      ReturnTargets rt, int out_row_bytes, const int* epoch_counter, int* __restrict__ begins,
                      int* __restrict__ ends, unsigned long long* __restrict__ c_table, int* status) {
   __shared__ int s_ok;
+  pdl_launch_dependents();
+  pdl_wait();  // the epoch was advanced by the dispatch before this kernel
   const int epoch = *epoch_counter;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -153,12 +157,16 @@ ep_wait_build_kernel(const int* arrive_flags, const int* meta, int per, int R, i
 }
 
 __global__ void ep_signal_kernel(ReturnTargets rt, int R, const int* epoch_counter) {
+  pdl_launch_dependents();
+  pdl_wait();  // every result row of the kernel before this one has been stored
   const int epoch = *epoch_counter;
   __threadfence_system();
   if (threadIdx.x < R) st_release_sys(rt.flag[threadIdx.x], epoch);
 }
 
 __global__ void ep_wait_kernel(const int* flags, int n, const int* epoch_counter, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int epoch = *epoch_counter;
   if (threadIdx.x < n && !wait_flag(flags + threadIdx.x, epoch)) *status = DS_TIMEOUT_FLAG;
 }
@@ -191,10 +199,9 @@ extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* w
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
   int blocks = m < 1 ? 1 : (m < sms * 4 ? m : sms * 4);
-  ep_dispatch_kernel<<<blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(h), token, static_cast<const unsigned short*>(wsorted), offsets, m, experts_per_rank,
-      n_ranks, row_bytes / 16, capacity, tg, done_counter, epoch_counter, status);
-  return check_cuda(cudaGetLastError(), "ep_dispatch launch");
+  return launch_kernel(ep_dispatch_kernel, blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream), "ep_dispatch launch",
+                       static_cast<const uint4*>(h), token, static_cast<const unsigned short*>(wsorted), offsets, m,
+                       experts_per_rank, n_ranks, row_bytes / 16, capacity, tg, done_counter, epoch_counter, status);
 }
 
 extern "C" int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
@@ -211,10 +218,9 @@ extern "C" int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta
   }
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
-  ep_wait_build_kernel<<<1, EP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      arrive_flags, meta, experts_per_rank, n_ranks, capacity, rt, out_row_bytes, epoch_counter, begins, ends,
-      reinterpret_cast<unsigned long long*>(c_table), status);
-  return check_cuda(cudaGetLastError(), "ep_wait_build launch");
+  return launch_kernel(ep_wait_build_kernel, 1, EP_THREADS, 0, static_cast<cudaStream_t>(stream), "ep_wait_build launch",
+                       arrive_flags, meta, experts_per_rank, n_ranks, capacity, rt, out_row_bytes, epoch_counter, begins,
+                       ends, reinterpret_cast<unsigned long long*>(c_table), status);
 }
 
 extern "C" int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t* epoch_counter, void* stream) {
@@ -226,8 +232,8 @@ extern "C" int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t
     rt.flag[s] = flag_dst[s];
     SY_REQUIRE(rt.flag[s], "ep_signal: null flag for rank %d", s);
   }
-  ep_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(rt, n_ranks, epoch_counter);
-  return check_cuda(cudaGetLastError(), "ep_signal launch");
+  return launch_kernel(ep_signal_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), "ep_signal launch", rt, n_ranks,
+                       epoch_counter);
 }
 
 extern "C" int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, void* stream) {
@@ -235,8 +241,8 @@ extern "C" int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_coun
   SY_REQUIRE(flags && epoch_counter && n >= 1 && n <= 32, "ep_wait: bad arguments");
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
-  ep_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, n, epoch_counter, status);
-  return check_cuda(cudaGetLastError(), "ep_wait launch");
+  return launch_kernel(ep_wait_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), "ep_wait launch", flags, n,
+                       epoch_counter, status);
 }
 
 // ---- CUDA IPC helpers: how the ranks' windows are mapped into one another (set-up time) ----
