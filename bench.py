@@ -14,8 +14,9 @@ in rotation), so a pass never finds its weights in L2.
           replayed from a CUDA graph;
   e2e     the same through the public Python API with HOST buffers: hidden states copied from
           pinned memory, `kernels.moe_layer`, result copied back, every pass;
-  roofline the dominant kernel (the SwiGLU weight stream of T=64) alone: algorithmic bytes per
-          launch / its CUDA-event duration, against the measured HBM copy bandwidth;
+  roofline the dominant kernel (the fused expert FFN of T=64: both weight streams in one launch)
+          alone: algorithmic bytes per launch / its CUDA-event duration, against the measured
+          HBM copy bandwidth;
   cpu_baseline / --impl reference: the float32 expert loop of the CPU oracle on the same
           sweep, on the host cores.
 
@@ -37,7 +38,6 @@ sys.path.insert(0, ROOT)
 SWEEP = (1, 8, 32, 64)
 H, I, E, TOPK = 2048, 1024, 64, 8
 EXPERT_BYTES = 3 * H * I * 2          # fp16 bytes of one expert's weights
-GATE_UP_BYTES = 2 * H * I * 2
 LAYERS = 8                             # resident weight sets used in rotation (8 x 805 MB)
 METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
 
@@ -268,7 +268,8 @@ def run_single_gpu(args):
     e2e_ms = e0.elapsed_time(e1)
     io_bytes = sum(T * H * 2 for T in SWEEP)
 
-    # ---- the dominant kernel alone: SwiGLU weight stream of T=64, one launch per layer in rotation
+    # ---- the dominant kernel alone: the fused expert FFN (both weight streams) of T=64, one
+    # launch per weight set in rotation, CUDA events around each launch on the launch stream
     T = SWEEP[-1]
     ext = kernels.ext()
     kern_ms, kern_bytes = [], []
@@ -277,18 +278,18 @@ def run_single_gpu(args):
         for l, (router, gu, dn) in enumerate(layers):
             idx, w = kernels.route(hs[T], router, TOPK, False)
             counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, E)
-            sorted_in.append((token, offsets))
+            sorted_in.append((token, offsets, wsorted))
         for rep in range(max(args.steps, 8) + 3):
             l = rep % LAYERS
-            token, offsets = sorted_in[l]
+            token, offsets, wsorted = sorted_in[l]
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            ext.grouped_gemv(hs[T], token, layers[l][1], offsets, T * TOPK, True, None)
+            ext.expert_ffn(hs[T], token, layers[l][1], layers[l][2], offsets, T * TOPK, wsorted, 0)
             b.record(stream)
             stream.synchronize()
             if rep >= 3:
                 kern_ms.append(a.elapsed_time(b))
-                kern_bytes.append(used[(T, l)] * GATE_UP_BYTES)
+                kern_bytes.append(used[(T, l)] * EXPERT_BYTES)
     peak, peak_src = peaks()
     achieved = sum(kern_bytes) / (sum(kern_ms) / 1e3) / 1e9
     assert ext.device_status(dev) == 0
@@ -313,10 +314,10 @@ def run_single_gpu(args):
         "e2e": {"value": e2e_bytes / (e2e_ms / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                 "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms / args.steps,
                 "api": "switchyard_b200.kernels.moe_layer, eager, host buffers pinned"},
-        "gpu_launches": args.steps * len(SWEEP) * 5,
+        "gpu_launches": args.steps * len(SWEEP) * 4,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, SWIGLU, streaming shape> (sy_grouped_gemv)",
-                     "workload": "T=64 gate/up projection, one launch per layer in rotation",
+                     "traffic": None, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, streaming shape>, fused FFN (sy_expert_ffn)",
+                     "workload": "T=64, gate/up + down projections of one layer in one launch, weight sets in rotation",
                      "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
                      "vs_nominal_8TBps": achieved / 8000.0},
         "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": threads, "kind": "port",

@@ -65,6 +65,15 @@ int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n
                       int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
                       void* scratch, size_t scratch_bytes, void* stream);
 
+/* route_sort — sy_route followed by sy_sort_by_expert in ONE launch, for decode-sized batches
+ * (n_tokens * top_k <= sy_route_sort_max_choices() = 8192, n_experts <= 128): one block routes all
+ * tokens and then sorts the choices it has just written. Outputs are those of the two separate
+ * calls, bit for bit (moe_kernels.cu:73-89 and 142-157 in one step). */
+int sy_route_sort_max_choices(void);
+int sy_route_sort(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
+                  int32_t* idx, void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
+                  int32_t* pos_of, void* stream);
+
 /* sort_by_expert_static — no counterpart in the reference. The same sort, same outputs bit for
  * bit, for callers that are not allowed to allocate device memory while they run and so
  * cannot provide scratch: a server that has handed all free HBM to its own arena (cudaMalloc

@@ -176,6 +176,10 @@ class _Ext:
     def sort_by_expert(self, idx, w, E):
         return list(mo.sort_by_expert(idx, w, E))
 
+    def route_sort(self, logits, k, norm):
+        idx, w = mo.route_kernel_rule(logits, k, norm)
+        return [idx, w] + list(mo.sort_by_expert(idx, w, logits.shape[1]))
+
     def combine(self, y, pos_of, idx, n_tokens):
         return mo.combine_expert_order(y, pos_of, idx, n_tokens)
 

@@ -5,11 +5,12 @@
 // maximum and the sum of exp(v - max) are float32 xor-butterflies; selection runs on the exp
 // values, larger first and the LOWER expert index on equal values; weights are exp / sum,
 // divided by the sum of the picked weights when renormalising, rounded once to 16 bits.
-#include "common.cuh"
+#include "route.cuh"
 
 namespace sy {
 
 constexpr int ROUTE_THREADS = 256;
+
 
 template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(ROUTE_THREADS)
@@ -20,66 +21,7 @@ route_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int norm,
   const int lane = threadIdx.x & 31;
   const int token = (blockIdx.x * ROUTE_THREADS + threadIdx.x) >> 5;
   if (token >= n_tokens) return;
-  const T* row = logits + (size_t)token * E;
-
-  float v[PER_LANE];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    int e = lane + 32 * j;
-    v[j] = e < E ? Elem<T>::to_f(row[e]) : -INFINITY;
-    mx = fmaxf(mx, v[j]);
-  }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-
-  float sum = 0.f;
-#pragma unroll
-  for (int j = 0; j < PER_LANE; ++j) {
-    int e = lane + 32 * j;
-    v[j] = e < E ? expf(v[j] - mx) : 0.f;
-    sum += v[j];
-  }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-
-  // k rounds of warp arg-max; lane r keeps round r's pick so that the stores are coalesced
-  float my_w = 0.f, total = 0.f;
-  int my_e = 0;
-  for (int r = 0; r < k; ++r) {
-    float best = -1.f;
-    int best_e = 1 << 30;
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j) {
-      int e = lane + 32 * j;
-      if (e < E && (v[j] > best || (v[j] == best && e < best_e))) {
-        best = v[j];
-        best_e = e;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) {
-        best = ob;
-        best_e = oe;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < PER_LANE; ++j)
-      if (lane + 32 * j == best_e) v[j] = -1.f;  // taken
-    float p = best / sum;
-    total += p;
-    if (lane == r) {
-      my_w = p;
-      my_e = best_e;
-    }
-  }
-  if (lane < k) {
-    idx[(size_t)token * k + lane] = my_e;
-    w[(size_t)token * k + lane] = Elem<T>::from_f(norm ? my_w / total : my_w);
-  }
+  route_token<T, PER_LANE>(logits + (size_t)token * E, E, k, norm, lane, idx + (size_t)token * k, w + (size_t)token * k);
 }
 
 template <typename T>

@@ -16,7 +16,7 @@
 // which reads the whole list once per expert and calls torch for the prefix sum in between.
 #include <mutex>
 
-#include "common.cuh"
+#include "route.cuh"
 
 namespace sy {
 
@@ -49,7 +49,7 @@ static SortShape sort_shape(int m) {
 }
 
 // Per-warp expert counts of this block's chunk into wcount[warp][e] (shared, zeroed here).
-__device__ __forceinline__ void count_chunk(const int* __restrict__ idx, int m, int begin, int per_warp, int E,
+__device__ __forceinline__ void count_chunk(const int* idx, int m, int begin, int per_warp, int E,
                                             int* wcount) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < SORT_WARPS * E; i += SORT_THREADS) wcount[i] = 0;
@@ -86,7 +86,7 @@ __device__ __forceinline__ void warp_scan_experts(const int* v, int E, int* out)
 }
 
 template <typename T>
-__device__ __forceinline__ void scatter_chunk(const int* __restrict__ idx, const T* __restrict__ w, int m, int k,
+__device__ __forceinline__ void scatter_chunk(const int* idx, const T* w, int m, int k,
                                               int begin, int per_warp, int E, int* wbase,
                                               int* __restrict__ token, T* __restrict__ wsorted,
                                               int* __restrict__ pos_of, int* status) {
@@ -137,6 +137,49 @@ sort_single_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, 
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
   // wcount[warp][e] <- first row of warp's rows of expert e
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int at = off[e];
+    for (int wi = 0; wi < SORT_WARPS; ++wi) {
+      int c = wcount[wi * E + e];
+      wcount[wi * E + e] = at;
+      at += c;
+    }
+  }
+  __syncthreads();
+  scatter_chunk<T>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
+}
+
+// Decode-sized batches: routing and the sort in ONE block and one launch. The block's warps
+// route the tokens (same arithmetic as route_kernel), the block synchronises, and the sort
+// proceeds on the indices it has just written. Saves a launch where launches are what the
+// layer's small kernels cost.
+template <typename T>
+__global__ void __launch_bounds__(SORT_THREADS)
+route_sort_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int norm, int per_block, int* idx, T* w,
+                  int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ token,
+                  T* __restrict__ wsorted, int* __restrict__ pos_of, int* status) {
+  extern __shared__ int sh[];
+  int* wcount = sh;                       // [SORT_WARPS][E]
+  int* total = wcount + SORT_WARPS * E;   // [E]
+  int* off = total + E;                   // [E + 1]
+  const int per_warp = per_block / SORT_WARPS;
+  const int m = n_tokens * k;
+  pdl_launch_dependents();
+  pdl_wait();  // the logits come from the router GEMM before this kernel
+  for (int t = threadIdx.x >> 5; t < n_tokens; t += SORT_WARPS)
+    route_token_any<T>(logits + (size_t)t * E, E, k, norm, threadIdx.x & 31, idx + (size_t)t * k, w + (size_t)t * k);
+  __syncthreads();  // the block's own global writes are visible to the block after the barrier
+  count_chunk(idx, m, 0, per_warp, E, wcount);
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int s = 0;
+    for (int wi = 0; wi < SORT_WARPS; ++wi) s += wcount[wi * E + e];
+    total[e] = s;
+    counts[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) warp_scan_experts(total, E, off);
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
   for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
     int at = off[e];
     for (int wi = 0; wi < SORT_WARPS; ++wi) {
@@ -256,6 +299,35 @@ extern "C" int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int t
              ? launch_sort<__half>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch, s)
              : launch_sort<__nv_bfloat16>(idx, w, m, top_k, n_experts, counts, offsets, token, wsorted, pos_of, scratch,
                                           s);
+}
+
+extern "C" int sy_route_sort_max_choices(void) { return sy::SORT_SINGLE_MAX; }
+
+extern "C" int sy_route_sort(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
+                             int32_t* idx, void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
+                             int32_t* pos_of, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_tokens >= 1 && n_experts >= 1 && n_experts <= 128 && top_k >= 1 && top_k <= 8 && top_k <= n_experts,
+             "route_sort: 1..128 experts, top-8, at least one token (got N=%d, E=%d, k=%d)", n_tokens, n_experts, top_k);
+  SY_REQUIRE((long long)n_tokens * top_k <= SORT_SINGLE_MAX, "route_sort: at most %d choices (got %lld)",
+             SORT_SINGLE_MAX, (long long)n_tokens * top_k);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "route_sort: dtype must be f16 or bf16");
+  SY_REQUIRE(logits && idx && w && counts && offsets && token && wsorted && pos_of, "route_sort: null pointer");
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  const int m = n_tokens * top_k;
+  const SortShape sh = sort_shape(m);
+  const size_t smem = (size_t)(SORT_WARPS * n_experts + 3 * n_experts + 1) * sizeof(int);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == SY_DTYPE_F16)
+    return launch_kernel(route_sort_kernel<__half>, 1, SORT_THREADS, smem, s, "route_sort launch",
+                         static_cast<const __half*>(logits), n_tokens, n_experts, top_k, norm_topk_prob, sh.per_block,
+                         idx, static_cast<__half*>(w), counts, offsets, token, static_cast<__half*>(wsorted), pos_of,
+                         status);
+  return launch_kernel(route_sort_kernel<__nv_bfloat16>, 1, SORT_THREADS, smem, s, "route_sort launch",
+                       static_cast<const __nv_bfloat16*>(logits), n_tokens, n_experts, top_k, norm_topk_prob,
+                       sh.per_block, idx, static_cast<__nv_bfloat16*>(w), counts, offsets, token,
+                       static_cast<__nv_bfloat16*>(wsorted), pos_of, status);
 }
 
 // ---- sort_by_expert_static: the same sort for callers that cannot hand over scratch ----------

@@ -162,8 +162,11 @@ class DistributedExpertParallel:
         logits = self.backend.linear(h, router)
         if self.bias is not None:
             logits = logits + self.bias
-        idx, w = ext.route(logits.contiguous(), self.k, self.norm)
-        counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, self.E)
+        if 0 < N * self.k <= kernels.ROUTE_SORT_MAX_CHOICES and self.E <= 128:
+            idx, w, counts, offsets, token, wsorted, pos_of = ext.route_sort(logits.contiguous(), self.k, self.norm)
+        else:
+            idx, w = ext.route(logits.contiguous(), self.k, self.norm)
+            counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, self.E)
         M = N * self.k
         code = _lib.SY_DTYPE_F16 if self.dtype == torch.float16 else _lib.SY_DTYPE_BF16
         shape = 1 if self.mode == "gemm" else 0

@@ -140,6 +140,25 @@ class Ext:
                        "sort_by_expert")
         return [counts, offsets, token, wsorted, pos_of]
 
+    def route_sort(self, logits, k, norm):
+        """route + sort_by_expert in one launch (decode-sized batches): returns
+        [idx, w, counts, offsets, token, wsorted, pos_of], the same tensors the two calls give."""
+        _check(logits, "logits")
+        N, E = logits.shape
+        code = _dtype_code(logits, "route_sort")
+        dev, M = logits.device, N * k
+        ints = torch.empty(2 * E + 1 + 3 * M, dtype=torch.int32, device=dev)
+        counts, offsets = ints[:E], ints[E:2 * E + 1]
+        token, pos_of = ints[2 * E + 1:2 * E + 1 + M], ints[2 * E + 1 + M:2 * E + 1 + 2 * M]
+        idx = ints[2 * E + 1 + 2 * M:].view(N, k)
+        halves = torch.empty(2 * M, dtype=logits.dtype, device=dev)
+        w, wsorted = halves[:M].view(N, k), halves[M:]
+        with _Device(dev) as stream:
+            _lib.check(self.lib.sy_route_sort(_ptr(logits), N, E, int(k), int(bool(norm)), code, _ptr(idx), _ptr(w),
+                                              _ptr(counts), _ptr(offsets), _ptr(token), _ptr(wsorted), _ptr(pos_of),
+                                              stream), "route_sort")
+        return [idx, w, counts, offsets, token, wsorted, pos_of]
+
     def _grouped(self, fn, name, A, a_rows, B, offsets, rows, swiglu, scale):
         _check(A, "A"), _check(B, "B"), _check(offsets, "offsets")
         code = _dtype_code(A, name)
@@ -288,7 +307,20 @@ def experts(h, idx, w, gate_up, down, mode="auto"):
     return E.combine(y, pos_of, idx, N)
 
 
+ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what one block routes and sorts
+
+
 def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
-    """route + experts (switchyard/kernels.py:91-93)."""
+    """route + experts (switchyard/kernels.py:91-93). Decode-sized batches take the fused
+    route+sort launch; the results are bit-identical to route() followed by experts()."""
+    N, E = h.shape[0], gate_up.shape[0]
+    if 0 < N * top_k <= ROUTE_SORT_MAX_CHOICES and router.shape[0] <= 128:
+        X = ext()
+        idx, w, counts, offsets, token, wsorted, pos_of = X.route_sort(F.linear(h, router).contiguous(), top_k,
+                                                                        norm_topk_prob)
+        if mode == "auto":
+            mode = "gemv" if N <= AUTO_GEMV_MAX_TOKENS else "gemm"
+        y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode)
+        return X.combine(y, pos_of, idx, N)
     idx, w = route(h, router, top_k, norm_topk_prob)
     return experts(h, idx, w, gate_up, down, mode)

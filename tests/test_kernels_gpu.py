@@ -121,6 +121,20 @@ def test_sort_bf16_weights(K):
         assert torch.equal(got.cpu(), ref)
 
 
+@pytest.mark.parametrize("N,E,k,dtype", [(1, 64, 8, torch.float16), (64, 64, 8, torch.float16), (300, 128, 8, torch.bfloat16),
+                                         (1024, 64, 8, torch.float16), (77, 60, 4, torch.float16)])
+def test_route_sort_in_one_launch_equals_the_two_calls(K, N, E, k, dtype):
+    logits = cases.route_logits(E, N, dtype=dtype).to(DEV)
+    for norm in (False, True):
+        idx, w = K.ext().route(logits, k, norm)
+        want = [idx, w] + K.ext().sort_by_expert(idx, w, E)
+        got = K.ext().route_sort(logits, k, norm)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        K.ext().route_sort(cases.route_logits(64, 1025).to(DEV), 8, False)  # more than one block sorts
+
+
 # ------------------------------------------------------------------------------ combine
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("N,E,k,H", [(50, 16, 4, 24 * 8), (333, 64, 8, 256), (64, 64, 8, 2048), (1, 64, 8, 2048)])
