@@ -162,7 +162,7 @@ class DistributedExpertParallel:
         logits = self.backend.linear(h, router)
         if self.bias is not None:
             logits = logits + self.bias
-        if 0 < N * self.k <= kernels.ROUTE_SORT_MAX_CHOICES and self.E <= 128:
+        if 0 < N <= kernels.ROUTE_SORT_MAX_TOKENS and N * self.k <= kernels.ROUTE_SORT_MAX_CHOICES and self.E <= 128:
             idx, w, counts, offsets, token, wsorted, pos_of = ext.route_sort(logits.contiguous(), self.k, self.norm)
         else:
             idx, w = ext.route(logits.contiguous(), self.k, self.norm)

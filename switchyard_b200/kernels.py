@@ -307,14 +307,17 @@ def experts(h, idx, w, gate_up, down, mode="auto"):
     return E.combine(y, pos_of, idx, N)
 
 
-ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what one block routes and sorts
+ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what one block can route and sort
+# Measured on a B200: the one-block route+sort wins while every warp of the block routes at most
+# one token; beyond that the separate routing kernel (a warp per token, many blocks) is faster.
+ROUTE_SORT_MAX_TOKENS = 16
 
 
 def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
     """route + experts (switchyard/kernels.py:91-93). Decode-sized batches take the fused
     route+sort launch; the results are bit-identical to route() followed by experts()."""
     N, E = h.shape[0], gate_up.shape[0]
-    if 0 < N * top_k <= ROUTE_SORT_MAX_CHOICES and router.shape[0] <= 128:
+    if 0 < N <= ROUTE_SORT_MAX_TOKENS and N * top_k <= ROUTE_SORT_MAX_CHOICES and router.shape[0] <= 128:
         X = ext()
         idx, w, counts, offsets, token, wsorted, pos_of = X.route_sort(F.linear(h, router).contiguous(), top_k,
                                                                         norm_topk_prob)
