@@ -406,6 +406,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
     if (lane == 0) {
       int it = 0, cursor = 0, seen = 0;
       bool alive = true;
+      // streaming shape: an expert's weights are read once, so they are marked evict-first in L2
+      const uint64_t policy = l2_policy_evict_first();
       for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
         const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
         const Problem& P = args.p[tile.phase];
@@ -425,8 +427,13 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
 #pragma unroll
           for (int a = 0; a < S::KATOMS; ++a) {
             const int kx = kb * S::BK + a * GM_ATOM_K;
-            tma_load_2d(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s]);
-            tma_load_2d(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s]);
+            if (PAIR) {
+              tma_load_2d(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s]);
+              tma_load_2d(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s]);
+            } else {
+              tma_load_2d_hint(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s], policy);
+              tma_load_2d_hint(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s], policy);
+            }
           }
         }
       }
