@@ -358,7 +358,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] - run one small layer shape (for profiling)")
-    ap.add_argument("--config", default="decode", choices=["decode", "ep256", "prefill"],
+    ap.add_argument("--config", default="decode", choices=["decode", "ep256", "prefill", "model"],
                     help="decode = the bench line (configs[1]); ep256 / prefill = configs[2] / configs[3], reported in DESIGN.md")
     args = ap.parse_args()
     if args.case:
@@ -370,7 +370,7 @@ def main():
         sys.exit("bench.py needs a CUDA GPU (there is no CPU path); use --impl reference for the CPU baseline")
     if args.config != "decode":
         from switchyard_b200 import bench_ep
-        return bench_ep.run_config(args)
+        return bench_ep.run_model(args) if args.config == "model" else bench_ep.run_config(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single_gpu(args)
     from switchyard_b200 import bench_ep

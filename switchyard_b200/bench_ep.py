@@ -264,3 +264,64 @@ def run_config(args):
                           "results": out, "device_status": kernels.ext().device_status(dev)}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------
+# config 5: the full random-init OLMoE-1B-7B architecture, fp16: 128-token prompts of uniform
+# random ids, 32 greedy decode tokens, `batch` requests dealt round-robin to the ranks
+# (attention data-parallel, experts expert-parallel). tok/s = batch * new / wall(generate),
+# prefill included, as the reference's bench/serve.py:81-85 computes it; decode-only tok/s too.
+def run_model(args):
+    import time
+    from . import kernels, olmoe
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = olmoe.Config()
+    per = c.experts // world
+    dtype, new, plen = torch.float16, 32, 128
+    w = olmoe.random_weights(c, dev, dtype, seed=0, experts=range(rank * per, (rank + 1) * per))
+    results = []
+    for batch in (8, 64):
+        if batch % world:
+            continue
+        mine = batch // world
+        g = torch.Generator().manual_seed(7)
+        prompts = [torch.randint(0, c.vocab, (plen,), generator=g).tolist() for _ in range(batch)][rank::world]
+        if world > 1:
+            from .ep_dist import DistributedExpertParallel
+            ep = DistributedExpertParallel(c.experts, c.top_k, c.norm_topk_prob, c.hidden, c.intermediate,
+                                           max_tokens=mine * plen, dtype=dtype, mode="auto", device=dev)
+            moe = lambda i, h: ep.layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"], w["layers"][i]["down"])
+        else:
+            moe = lambda i, h: kernels.moe_layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
+                                                 w["layers"][i]["down"], c.top_k, c.norm_topk_prob)
+        dec = olmoe.Decoder(c, w, moe)
+        dec.generate(prompts, 4, graph=True)  # warm-up (libraries, allocator, graph capture path)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        marks = []
+        t0 = time.perf_counter()
+        out = dec.generate(prompts, new, graph=True, marks=marks)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        times = torch.tensor([t1 - t0, marks[1][1] - marks[0][1]], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+            ep.close()
+        wall, decode = float(times[0]), float(times[1])
+        results.append({"batch": batch, "requests_per_gpu": mine, "wall_s": wall, "tok_per_s": batch * new / wall,
+                        "decode_tok_per_s": batch * (new - 1) / decode, "ms_per_decode_step": decode / (new - 1) * 1e3,
+                        "first_tokens": out[0][:4]})
+    if rank == 0:
+        print(json.dumps({"config": "model", "model": "OLMoE-1B-7B architecture, random init, fp16", "n_gpus": world,
+                          "prompt_tokens": plen, "new_tokens": new, "parallelism": f"dp{world} attention, ep{world} experts",
+                          "decode": "one CUDA graph per decode step (all layers)", "results": results,
+                          "device_status": kernels.ext().device_status(dev)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()

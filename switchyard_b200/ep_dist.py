@@ -96,7 +96,7 @@ class DistributedExpertParallel:
         self.group = group
         self.rank, self.R = dist.get_rank(group), dist.get_world_size(group)
         assert num_experts % self.R == 0, "experts must split evenly over the ranks"
-        assert mode in ("gemv", "gemm"), "the distributed layer takes an explicit mode"
+        assert mode in ("gemv", "gemm", "auto"), "mode: gemv, gemm, or auto (by this rank's token count)"
         self.E, self.per, self.k, self.norm = num_experts, num_experts // self.R, top_k, norm_topk_prob
         self.H, self.I, self.dtype, self.mode = hidden, inter, dtype, mode
         self.backend = backend if backend is not None else CudaBackend(device)
@@ -169,7 +169,10 @@ class DistributedExpertParallel:
             counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, self.E)
         M = N * self.k
         code = _lib.SY_DTYPE_F16 if self.dtype == torch.float16 else _lib.SY_DTYPE_BF16
-        shape = 1 if self.mode == "gemm" else 0
+        mode = self.mode
+        if mode == "auto":  # rows per expert ~ tokens * ranks * k / E; keep 4x headroom for skew within a 64-row tile
+            mode = "gemv" if N * self.R * self.k * 4 <= 64 * self.E else "gemm"
+        shape = 1 if mode == "gemm" else 0
         with self.backend.stream() as stream:
             _lib.check(lib.sy_ep_dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M, per,
                                           R, H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst, self.arrive_dst,
