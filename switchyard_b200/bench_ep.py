@@ -301,13 +301,14 @@ def run_model(args):
             moe = lambda i, h: kernels.moe_layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
                                                  w["layers"][i]["down"], c.top_k, c.norm_topk_prob)
         dec = olmoe.Decoder(c, w, moe)
-        dec.generate(prompts, 4, graph=True)  # warm-up (libraries, allocator, graph capture path)
+        session = olmoe.Session(dec, mine, plen + new)
+        dec.generate(prompts, 4, graph=True, session=session)  # warm-up: libraries, allocator, graph capture
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         marks = []
         t0 = time.perf_counter()
-        out = dec.generate(prompts, new, graph=True, marks=marks)
+        out = dec.generate(prompts, new, graph=True, marks=marks, session=session)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         times = torch.tensor([t1 - t0, marks[1][1] - marks[0][1]], dtype=torch.float64, device=dev)

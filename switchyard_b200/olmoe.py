@@ -228,11 +228,13 @@ class Decoder:
         return F.linear(rmsnorm(x, W["final_norm"], c.rms_eps), W["lm_head"])[:, 0]
 
     @torch.no_grad()
-    def generate(self, prompts, max_new_tokens, graph=False, marks=None):
+    def generate(self, prompts, max_new_tokens, graph=False, marks=None, session=None):
         """Greedy decoding of a batch of token lists (left-padded internally); returns the new
-        tokens per prompt. graph=True replays the decode step from a CUDA graph. marks: optional
-        list that receives a callable-free timeline [("prefill_done", t), ("decode_done", t)] of
-        time.perf_counter() values taken after a device synchronisation."""
+        tokens per prompt. graph=True replays the decode step from a CUDA graph; pass a `Session`
+        to keep the cache and the captured graph across calls of the same batch size. marks:
+        optional list that receives ("prefill_done", t) and ("decode_done", t), time.perf_counter()
+        values taken after the device has finished."""
+        import time
         dev, dtype = self.w["embed"].device, self.w["embed"].dtype
         B, P = len(prompts), max(len(p) for p in prompts)
         tokens = torch.zeros(B, P, dtype=torch.int64, device=dev)
@@ -240,46 +242,54 @@ class Decoder:
         for b, p in enumerate(prompts):
             tokens[b, P - len(p):] = torch.tensor(p, device=dev)
             valid[b, P - len(p):] = True
-        cache = Cache(self.c, B, P + max_new_tokens, dtype, dev)
+        if session is None:
+            session = Session(self, B, P + max_new_tokens)
+        session.reset()
+        cache = session.cache
+        assert cache.k[0].shape[0] == B and cache.capacity >= P + max_new_tokens
         nxt = self.forward(tokens, cache, valid)[:, -1].argmax(-1)
         out = [nxt]
         if marks is not None:
-            import time
-            torch.cuda.synchronize() if dev.type == "cuda" else None
+            if dev.type == "cuda":
+                torch.cuda.synchronize()
             marks.append(("prefill_done", time.perf_counter()))
-        step = DecodeGraph(self, cache, B) if graph and dev.type == "cuda" else None
         for _ in range(max_new_tokens - 1):
-            logits = step(nxt) if step is not None else self.decode_step(nxt, cache)
+            logits = session.step(nxt) if graph and dev.type == "cuda" else self.decode_step(nxt, cache)
             nxt = logits.argmax(-1)
             out.append(nxt)
         result = torch.stack(out, 1).tolist()  # one transfer; also waits for the device
         if marks is not None:
-            import time
             marks.append(("decode_done", time.perf_counter()))
         return result
 
 
-class DecodeGraph:
-    """One decode step captured in a CUDA graph (all layers: attention and MoE). Every rank of
-    an expert-parallel group must capture and replay in lockstep."""
+class Session:
+    """A KV cache of fixed batch and capacity plus the decode step captured over it in a CUDA
+    graph (all layers: attention and MoE). Reused across generate() calls; every rank of an
+    expert-parallel group must create, capture and replay in lockstep."""
 
-    def __init__(self, decoder, cache, batch):
-        self.tokens = torch.zeros(batch, dtype=torch.int64, device=decoder.w["embed"].device)
-        self.decoder, self.cache = decoder, cache
-        self.graph, self.logits = None, None
+    def __init__(self, decoder, batch, capacity):
+        w = decoder.w["embed"]
+        self.decoder = decoder
+        self.cache = Cache(decoder.c, batch, capacity, w.dtype, w.device)
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=w.device)
+        self.graph, self.logits, self.warm = None, None, False
 
-    def __call__(self, tokens):
+    def reset(self):
+        c = self.cache
+        c.valid.zero_()  # stale keys and values stay but are masked out
+        c.next_pos.zero_()
+        c.length.zero_()
+
+    def step(self, tokens):
         self.tokens.copy_(tokens)
         if self.graph is None:
-            # the first step runs eagerly (it also warms every library up), the second is captured
-            if self.logits is None:
-                self.logits = self.decoder.decode_step(self.tokens, self.cache)
-                return self.logits.clone()
+            if not self.warm:  # the first step runs eagerly (it warms every library up)
+                self.warm = True
+                return self.decoder.decode_step(self.tokens, self.cache)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
                 self.logits = self.decoder.decode_step(self.tokens, self.cache)
-            self.graph.replay()  # capture does not execute: this replay is the captured step
-            return self.logits
-        self.graph.replay()
+        self.graph.replay()  # (capture does not execute: the replay is the step)
         return self.logits
