@@ -1,14 +1,6 @@
 // grouped_gemm and grouped_gemv: every expert's slice of the sorted batch on the tcgen05 tensor
-// cores. One kernel in two shapes (see Shape below): "gemm" for compute-bound batches, "gemv"
-// for decode, where the layer is a stream over expert weights.
-//
-// Orientation. The weight tile is the MMA's M operand and the token rows are its N operand
-// ("C^T = W . X^T"): an instruction multiplies 128 weight rows by up to 128 token rows over 16
-// k. That keeps M = 128 full no matter how few rows an expert has, so the same code is a
-// weight stream for a handful of rows and a GEMM for thousands; N is rounded up to a multiple
-// of 16 per tile. (A CUDA-core weight stream was built first and measured on a B200: float32
-// FMA keeps up with HBM3e only below about four rows per expert, 1.2 TB/s at 64 tokens, so the
-// decode path streams through the tensor cores too.)
+// cores. One persistent kernel in three shapes (see Shape below): "gemv" streams expert weights
+// past a handful of token rows (decode), "gemm" is the compute-bound shape, alone or as CTA pairs.
 //
 // One tile = (expert, a block of token rows, a block of output columns). The grid is
 // persistent (one block per SM); tiles are numbered on the device from `offsets` (expert-major,
@@ -16,21 +8,28 @@
 // and dealt round-robin, so nothing about the batch is read back to the host.
 //
 // A block is fourteen warps with fixed roles, connected by mbarriers:
-//   warp 0      TMA producer: the weight tiles of each k block, 128-byte swizzle;
-//   warps 2-9   gather producers: the tile's token rows, picked from the UNSORTED activations
-//               through a_rows, 16-byte cp.async copies straight into the same swizzled layout,
-//               several k blocks in flight per thread;
+//   warp 0      TMA producer: the weight boxes of each k block (128-byte swizzle) and, when a
+//               tile's token rows are contiguous in memory (no a_rows, one range per expert),
+//               the token box too;
+//   warps 2-9   gather producers, for token rows that are NOT contiguous (picked from the
+//               unsorted activations through a_rows, or spread over several ranges): 16-byte
+//               cp.async copies straight into the same swizzled layout; idle otherwise;
 //   warp 1      MMA issuer: one thread, tcgen05.mma into one of two accumulator buffers in
 //               tensor memory; tcgen05.commit releases the stage / publishes the accumulators;
-//   warps 10-13 epilogue: tcgen05.ld of the accumulators (a thread owns one output column and
-//               walks the token rows), SwiGLU or router-weight scaling with the 16-bit
-//               rounding points, results staged in shared memory and written out as whole
-//               128/256-byte row segments (16 bytes per thread; the destination may be a peer
-//               GPU). It overlaps the next tile's main loop.
+//   warps 10-13 epilogue: tcgen05.ld of the accumulators, SwiGLU or router-weight scaling with
+//               the 16-bit rounding points, stores to C or to per-range destinations (a peer
+//               GPU's mailbox). It overlaps the next tile's main loop.
 //
 // An output element is a sum over k in instruction order that does not depend on which other
-// rows share the tile or on the tile's N, so a row's bits are the same on one GPU and inside
-// an expert-parallel segment (within one shape; the two shapes are separate modes).
+// rows share the tile, so a row's bits are the same on one GPU and inside an expert-parallel
+// segment (within one mode).
+//
+// What was measured on a B200 and dropped: a CUDA-core weight stream (float32 FMA keeps up with
+// HBM3e only below about four rows per expert); TMA row gather (tile::gather4) for the token
+// rows (about 47 ns per four-row instruction per SM: a quarter of what the compute shape needs);
+// one cp.async gather for all rows with a thread-blocking wait per stage (the wait serialised
+// the stages). Gathering 16-byte pieces through the load/store unit tops out near 960 TFLOP/s
+// for the whole kernel, which is why compute-bound callers sort the rows first.
 //
 // Replaces switchyard/csrc/moe_kernels.cu:159-298 (64x64x32 WMMA tiles, one block per tile,
 // tile list built by torch on the host) and l.306-415 (CUDA-core GEMV, one block per expert and
@@ -39,12 +38,29 @@
 
 #include <atomic>
 #include <mutex>
+#include <stdlib.h>
 #include <string.h>
 #include <type_traits>
 
 #include "common.cuh"
 
 namespace sy {
+
+// Profiling build only (-DSY_PROFILE, not part of the shipped library): blocks 0 and 1 add up
+// the clocks each role spends waiting and working; sy_prof_read returns the totals.
+#ifdef SY_PROFILE
+__device__ unsigned long long g_prof[32];
+#define PROF_T0 long long prof_t = clock64()
+#define PROF_ADD(i)                                                                       \
+  do {                                                                                    \
+    const long long prof_n = clock64();                                                   \
+    if (blockIdx.x < 2) atomicAdd(&g_prof[blockIdx.x * 16 + (i)], (unsigned long long)(prof_n - prof_t)); \
+    prof_t = prof_n;                                                                      \
+  } while (0)
+#else
+#define PROF_T0
+#define PROF_ADD(i)
+#endif
 
 constexpr int GM_ATOM_K = 64;                      // k per swizzle atom: 128-byte rows
 constexpr int GM_BM = 128;                         // weight rows per accumulator (UMMA M)
@@ -53,33 +69,44 @@ constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_GATHER_WARPS + GM_EPI_WARPS) * 32;
 constexpr int GM_MAX_E = 256;
 constexpr int GM_RING_BYTES = 192 * 1024;          // shared-memory ring of stages
+constexpr int GM_MAX_BN = 256;                      // most token rows in a tile (any shape)
 constexpr int GM_EPI_ROWS = 64;                    // token rows the epilogue stages per pass
 constexpr int GM_EPI_BYTES = GM_EPI_ROWS * GM_BM * 2;  // staged output tile: 64 rows x 128 columns
 constexpr int GM_SMEM = GM_RING_BYTES + GM_EPI_BYTES + 1024;  // + room to align the ring to 1024
 constexpr uint64_t GM_WAIT_NS = 1000000000ull;
 
-// Two shapes of the same kernel.
-//   PAIR   (mode "gemm"): 128 token rows per tile, two 128-row weight tiles sharing them (two
-//          accumulators), 48 KB stages x 4: the compute-bound shape.
-//   !PAIR  (mode "gemv"): 64 token rows per tile, one 128-row weight tile (with SwiGLU: 64 gate
-//          rows + 64 up rows of the same columns) over 128 k per stage (two swizzle atoms), so a
-//          stage carries the same 32 KB of weights and the same eight MMAs as a PAIR stage, but
-//          tiles are half as large and twice as many: less imbalance when every tile is one
-//          pass over an expert's weights.
-template <bool PAIR> struct Shape {
-  static constexpr int BN = PAIR ? 128 : 64;               // token rows per tile (UMMA N max)
-  static constexpr int BOX_ROWS = PAIR ? 128 : 64;         // weight rows per TMA box (two boxes per atom)
-  static constexpr int KATOMS = PAIR ? 1 : 2;              // 64-wide k atoms per stage
-  static constexpr int BK = KATOMS * GM_ATOM_K;            // k per stage
-  static constexpr int W_ATOM_BYTES = 2 * BOX_ROWS * 128;  // weight bytes of one atom (both boxes)
-  static constexpr int X_ATOM_BYTES = BN * 128;
-  static constexpr int W_BYTES = KATOMS * W_ATOM_BYTES;    // weight bytes per stage (32 KB either way)
+// Three shapes of the same kernel.
+//   SH_STREAM (mode "gemv"): the weight tile is the MMA's M operand (128 weight rows; with
+//            SwiGLU 64 gate rows + 64 up rows of the same columns) and up to 64 token rows are
+//            its N operand, rounded up to 16 per tile; 128 k per stage (two swizzle atoms). M
+//            stays full however few rows an expert has: a weight stream for a handful of rows.
+//   SH_PAIR  (mode "gemm"): the usual orientation. 128 token rows are M, 256 weight rows are N
+//            (with SwiGLU 128 gate + 128 up rows of the same columns): one 128x256x16 MMA per
+//            16 k, and an epilogue thread owns a token row, so it writes 16 bytes of a row at a
+//            time and needs no exchange for SwiGLU. 48 KB stages x 4.
+//   SH_DUO   (mode "gemm", many rows per expert): two CTAs on neighbouring SMs work as one
+//            (tcgen05 cta_group::2). A tile is 256 token rows (128 gathered by each CTA) by 256
+//            weight rows (128 loaded by each CTA); the pair's MMAs read both halves. Per MMA a
+//            CTA fills 2/3 of the shared memory a PAIR tile needs. 32 KB stages x 6.
+enum { SH_STREAM = 0, SH_PAIR = 1, SH_DUO = 2 };
+template <int SH> struct Shape {
+  static constexpr bool STREAM = SH == SH_STREAM, PAIR = SH == SH_PAIR, DUO = SH == SH_DUO;
+  static constexpr int BN = STREAM ? 64 : DUO ? 256 : 128;  // token rows per tile
+  static constexpr int XR = STREAM ? 64 : 128;              // token rows one CTA stages
+  static constexpr int WR = PAIR ? 256 : 128;               // weight rows one CTA stages
+  static constexpr int BOX_ROWS = WR / 2;                   // weight rows per TMA box (two boxes per atom)
+  static constexpr int KATOMS = STREAM ? 2 : 1;             // 64-wide k atoms per stage
+  static constexpr int BK = KATOMS * GM_ATOM_K;             // k per stage
+  static constexpr int W_ATOM_BYTES = WR * 128;             // weight bytes of one atom (both boxes)
+  static constexpr int X_ATOM_BYTES = XR * 128;
+  static constexpr int W_BYTES = KATOMS * W_ATOM_BYTES;     // weight bytes per stage
   static constexpr int X_BYTES = KATOMS * X_ATOM_BYTES;
-  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;     // 48 KB, or 32 KB for DUO
   static constexpr int STAGES = GM_RING_BYTES / STAGE_BYTES;
-  static constexpr int ACCS = PAIR ? 2 : 1;                // accumulators per tile
-  static constexpr int BUF_COLS = ACCS * BN;               // tensor-memory columns per buffer
-  static constexpr int TMEM_COLS = 2 * BUF_COLS;           // two buffers: 512 or 128
+  static constexpr int BUF_COLS = STREAM ? BN : 256;        // tensor-memory columns per accumulator buffer
+  static constexpr int TMEM_COLS = 2 * BUF_COLS;            // two buffers: 128 or 512
+  static constexpr int CTAS = DUO ? 2 : 1;                  // CTAs that share a tile
+  static constexpr int GATHER_GROUP = GM_GATHER_WARPS / STAGES;  // gather warps per slot of the ring
 };
 
 struct Tile {
@@ -91,12 +118,15 @@ struct Tile {
 // (gate/up with SwiGLU, then down with the router-weight scale) run by ONE launch.
 struct Problem {
   CUtensorMap map;                       // [experts * n_full, K] weights, box 64 k x BOX_ROWS
+  CUtensorMap xmap;                      // [rows, K] activations, box 64 k x XR; used when x_tma
   const void* A;
   const int* a_rows;
   const void* scale;
   void* C;
   const unsigned long long* c_table;     // optional per-range output row pointers
-  int Nout, K, swiglu, pad_;
+  int Nout, K, swiglu;
+  int x_tma;                             // A's rows are the ranges' rows themselves (no a_rows, one range per
+                                         // expert): a tile's rows are contiguous and come by TMA, not by gather
 };
 
 struct KernelArgs {
@@ -152,16 +182,16 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   return v;
 }
 
-// The epilogue of one tile, specialised on the epilogue kind so that its inner loops carry no
-// run-time switches: accumulators -> SwiGLU / router-weight scale / plain rounding -> memory.
-template <typename T, bool PAIR, bool SWIGLU, bool SCALE>
-__device__ __forceinline__ void epilogue_tile(const Tile& tile, int buf, uint32_t tmem, int q, int lane, int et, bool alive,
-                                              int& chunk_no, int Nout, int COLS, const T* __restrict__ scale,
-                                              T* __restrict__ C, const unsigned long long* __restrict__ c_table,
-                                              int group_div, const int* s_begin, const int* s_end, int* map_row_s,
-                                              int* map_grp_s, float (*s_xch)[GM_BM / 2][9], unsigned char* out_tile) {
-  using S = Shape<PAIR>;
-  constexpr int BN = S::BN;
+// The epilogue of one STREAM tile, specialised on the epilogue kind so that its inner loops
+// carry no run-time switches: accumulators -> SwiGLU / router-weight scale / plain rounding ->
+// memory. A thread owns one weight row (= output column) and walks the token rows.
+template <typename T, bool SWIGLU, bool SCALE>
+__device__ __forceinline__ void epilogue_stream(const Tile& tile, int buf, uint32_t tmem, int q, int lane, int et, bool alive,
+                                                int& chunk_no, int Nout, int colbase, const T* __restrict__ scale,
+                                                T* __restrict__ C, const unsigned long long* __restrict__ c_table,
+                                                int group_div, const int* s_begin, const int* s_end, int* map_row_s,
+                                                int* map_grp_s, float (*s_xch)[GM_BM / 2][9], unsigned char* out_tile) {
+  using S = Shape<SH_STREAM>;
   const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * S::BUF_COLS;
   const int wrow = q * 32 + lane;
   // With several ranges per expert the tile's rows in A / C space (and the range of each) are
@@ -169,48 +199,37 @@ __device__ __forceinline__ void epilogue_tile(const Tile& tile, int buf, uint32_
   const bool mapped = group_div > 1;
   const int row_base = s_begin[tile.e * group_div] + tile.row0;
   if (mapped) {
-    if (et < tile.nvalid) {
+    for (int i = et; i < tile.nvalid; i += GM_EPI_WARPS * 32) {
       int gr;
-      map_row_s[et] = map_row(tile.e, tile.row0 + et, group_div, s_begin, s_end, gr);
-      map_grp_s[et] = gr;
+      map_row_s[i] = map_row(tile.e, tile.row0 + i, group_div, s_begin, s_end, gr);
+      map_grp_s[i] = gr;
     }
     named_barrier_sync(3, GM_EPI_WARPS * 32);
   }
-  constexpr bool exchange = !PAIR && SWIGLU;  // one accumulator: gate rows in lanes 0-63, up rows in 64-127
+  constexpr bool exchange = SWIGLU;  // gate rows in lanes 0-63, up rows in 64-127
   if (!c_table) {
     // Local destination: every thread stores its own column's values directly (2 bytes per
     // store, a warp covers 64 contiguous bytes of a row); L2 merges them, and the epilogue
     // stays short enough to hide behind the next tile's main loop.
     if (!exchange) {
-      const int col0 = tile.cb * COLS + wrow;
-      const int col1 = col0 + GM_BM;  // the second accumulator's column (PAIR without SwiGLU)
+      const int col0 = colbase + wrow;
       for (int n0 = 0; n0 < tile.nvalid && alive; n0 += 8) {
-        uint32_t v0[8], v1[8];
+        uint32_t v0[8];
         tmem_ld_x8(taddr + n0, v0);
-        if (PAIR) tmem_ld_x8(taddr + BN + n0, v1);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          if (n0 + j < tile.nvalid) {
+          if (n0 + j < tile.nvalid && col0 < Nout) {
             const int row = mapped ? map_row_s[n0 + j] : row_base + n0 + j;
-            const float f0 = __uint_as_float(v0[j]), f1 = PAIR ? __uint_as_float(v1[j]) : 0.f;
-            if (SWIGLU) {
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_swiglu<T>(f0, f1);
-            } else if (SCALE) {
-              const T sc = scale[row];
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = epilogue_scale<T>(f0, sc);
-              if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = epilogue_scale<T>(f1, sc);
-            } else {
-              if (col0 < Nout) C[(size_t)row * Nout + col0] = Elem<T>::from_f(f0);
-              if (PAIR && col1 < Nout) C[(size_t)row * Nout + col1] = Elem<T>::from_f(f1);
-            }
+            const float f0 = __uint_as_float(v0[j]);
+            C[(size_t)row * Nout + col0] = SCALE ? epilogue_scale<T>(f0, scale[row]) : Elem<T>::from_f(f0);
           }
         }
       }
     } else {
       // Warps 2,3 (up rows) pass their values to warps 0,1 (gate rows) through shared memory.
       const int j64 = wrow & 63;
-      const int col = tile.cb * COLS + j64;
+      const int col = colbase + j64;
       for (int n0 = 0; n0 < tile.nvalid; n0 += 8, ++chunk_no) {
         uint32_t v[8];
         if (alive) {
@@ -241,77 +260,143 @@ __device__ __forceinline__ void epilogue_tile(const Tile& tile, int buf, uint32_
     constexpr int OC = exchange ? GM_BM / 2 : GM_BM;  // output columns per pass
     constexpr int ORB = OC * 2;                       // bytes per staged row
     constexpr int TPR = ORB / 16;                     // threads per row when copying out
-    constexpr int store_accs = (PAIR && !SWIGLU) ? 2 : 1;
 #pragma unroll 1
-    for (int acc = 0; acc < store_accs; ++acc) {
-#pragma unroll 1
-      for (int nb = 0; nb < tile.nvalid; nb += GM_EPI_ROWS) {
-        const int nrows = min(GM_EPI_ROWS, tile.nvalid - nb);
-        // ---- phase 1: tensor memory -> registers -> epilogue arithmetic -> staged tile
-        if (!exchange) {
-          for (int n0 = nb; n0 < nb + nrows; n0 += 8) {
-            uint32_t v0[8], v1[8];
-            if (alive) {
-              tmem_ld_x8(taddr + acc * BN + n0, v0);
-              if (SWIGLU) tmem_ld_x8(taddr + BN + n0, v1);
-              tmem_ld_wait();
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (alive && n0 + j < tile.nvalid) {
-                const float f0 = __uint_as_float(v0[j]);
-                T o;
-                if (SWIGLU) o = epilogue_swiglu<T>(f0, __uint_as_float(v1[j]));
-                else if (SCALE) o = epilogue_scale<T>(f0, scale[mapped ? map_row_s[n0 + j] : row_base + n0 + j]);
-                else o = Elem<T>::from_f(f0);
-                *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + wrow * 2) = o;
-              }
-            }
+    for (int nb = 0; nb < tile.nvalid; nb += GM_EPI_ROWS) {
+      const int nrows = min(GM_EPI_ROWS, tile.nvalid - nb);
+      // ---- phase 1: tensor memory -> registers -> epilogue arithmetic -> staged tile
+      if (!exchange) {
+        for (int n0 = nb; n0 < nb + nrows; n0 += 8) {
+          uint32_t v0[8];
+          if (alive) {
+            tmem_ld_x8(taddr + n0, v0);
+            tmem_ld_wait();
           }
-        } else {
-          const int j64 = wrow & 63;
-          for (int n0 = nb; n0 < nb + nrows; n0 += 8, ++chunk_no) {
-            uint32_t v[8];
-            if (alive) {
-              tmem_ld_x8(taddr + n0, v);
-              tmem_ld_wait();
-            }
-            float* slot = s_xch[chunk_no & 1][j64];
-            if (q >= 2 && alive) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
-            }
-            named_barrier_sync(2, GM_EPI_WARPS * 32);
-            if (q < 2 && alive) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (n0 + j < tile.nvalid)
-                  *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + j64 * 2) =
-                      epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
+          for (int j = 0; j < 8; ++j) {
+            if (alive && n0 + j < tile.nvalid) {
+              const float f0 = __uint_as_float(v0[j]);
+              T o;
+              if (SCALE) o = epilogue_scale<T>(f0, scale[mapped ? map_row_s[n0 + j] : row_base + n0 + j]);
+              else o = Elem<T>::from_f(f0);
+              *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + wrow * 2) = o;
             }
           }
         }
-        named_barrier_sync(3, GM_EPI_WARPS * 32);
-        // ---- phase 2: staged tile -> memory, 16 bytes per thread, whole row segments
-        const int col = tile.cb * COLS + acc * GM_BM + (et % TPR) * 8;
-        if (alive && col < Nout) {
-          for (int r = et / TPR; r < nrows; r += GM_EPI_WARPS * 32 / TPR) {
-            // c_table[g] is where row s_begin[g] of range g lands
-            const int gr = mapped ? map_grp_s[nb + r] : tile.e;
-            const int row = mapped ? map_row_s[nb + r] : row_base + nb + r;
-            T* dst = reinterpret_cast<T*>(c_table[gr]) + (size_t)(row - s_begin[gr]) * Nout + col;
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(out_tile + r * ORB + (et % TPR) * 16);
+      } else {
+        const int j64 = wrow & 63;
+        for (int n0 = nb; n0 < nb + nrows; n0 += 8, ++chunk_no) {
+          uint32_t v[8];
+          if (alive) {
+            tmem_ld_x8(taddr + n0, v);
+            tmem_ld_wait();
+          }
+          float* slot = s_xch[chunk_no & 1][j64];
+          if (q >= 2 && alive) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) slot[j] = __uint_as_float(v[j]);
+          }
+          named_barrier_sync(2, GM_EPI_WARPS * 32);
+          if (q < 2 && alive) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n0 + j < tile.nvalid)
+                *reinterpret_cast<T*>(out_tile + (n0 + j - nb) * ORB + j64 * 2) =
+                    epilogue_swiglu<T>(__uint_as_float(v[j]), slot[j]);
           }
         }
-        named_barrier_sync(3, GM_EPI_WARPS * 32);
       }
+      named_barrier_sync(3, GM_EPI_WARPS * 32);
+      // ---- phase 2: staged tile -> memory, 16 bytes per thread, whole row segments
+      const int col = colbase + (et % TPR) * 8;
+      if (alive && col < Nout) {
+        for (int r = et / TPR; r < nrows; r += GM_EPI_WARPS * 32 / TPR) {
+          // c_table[g] is where row s_begin[g] of range g lands
+          const int gr = mapped ? map_grp_s[nb + r] : tile.e;
+          const int row = mapped ? map_row_s[nb + r] : row_base + nb + r;
+          T* dst = reinterpret_cast<T*>(c_table[gr]) + (size_t)(row - s_begin[gr]) * Nout + col;
+          *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(out_tile + r * ORB + (et % TPR) * 16);
+        }
+      }
+      named_barrier_sync(3, GM_EPI_WARPS * 32);
     }
   }
 }
 
-template <typename T, bool PAIR>
+template <typename T> __device__ __forceinline__ uint32_t pack2(T a, T b) {
+  return (uint32_t) reinterpret_cast<const uint16_t&>(a) | ((uint32_t) reinterpret_cast<const uint16_t&>(b) << 16);
+}
+
+// The epilogue of one PAIR / DUO tile. A thread owns one TOKEN row of the tile (its lane of
+// tensor memory) and walks the output columns, sixteen at a time: SwiGLU pairs a gate column
+// with its up column from the same row, so nothing is exchanged between threads, and results
+// leave as 16-byte stores, two per step, to the row's place in C or behind c_table (a peer GPU).
+template <typename T, int SH, bool SWIGLU, bool SCALE>
+__device__ __forceinline__ void epilogue_rows(const Tile& tile, int buf, uint32_t tmem, int q, int lane, int cr, bool alive,
+                                              int Nout, int colbase, const T* __restrict__ scale, T* __restrict__ C,
+                                              const unsigned long long* __restrict__ c_table, int group_div,
+                                              const int* s_begin, const int* s_end) {
+  using S = Shape<SH>;
+  const int trow = cr * S::XR + q * 32 + lane;  // this thread's row of the tile
+  if (!alive || cr * S::XR + q * 32 >= tile.nvalid) return;  // the whole warp is past the tile's end
+  const bool valid = trow < tile.nvalid;
+  const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + buf * S::BUF_COLS;
+  T* dst = nullptr;
+  T sc = Elem<T>::from_f(0.f);
+  if (valid) {
+    int gr = tile.e * group_div, row;
+    if (group_div > 1) row = map_row(tile.e, tile.row0 + trow, group_div, s_begin, s_end, gr);
+    else row = s_begin[gr] + tile.row0 + trow;
+    // c_table[g] is where row s_begin[g] of range g lands
+    dst = (c_table ? reinterpret_cast<T*>(c_table[gr]) + (size_t)(row - s_begin[gr]) * Nout : C + (size_t)row * Nout) + colbase;
+    if (SCALE) sc = scale[row];
+  }
+  // Accumulator columns: SwiGLU tiles hold [gate | up] groups of G columns (PAIR: one group of
+  // 128 + 128; DUO: each CTA's weight rows are 64 + 64, so two groups); plain tiles hold the
+  // 256 output columns in order.
+  constexpr int G = S::DUO ? 64 : 128;
+  constexpr int OUT_COLS = SWIGLU ? 128 : 256;
+#pragma unroll 1
+  for (int oc = 0; oc < OUT_COLS; oc += 16) {
+    if (colbase + oc >= Nout) break;
+    uint32_t a[16], b[16];
+    if (SWIGLU) {
+      const int gc = (oc / G) * 2 * G + (oc % G);
+      tmem_ld_x8(taddr + gc, *reinterpret_cast<uint32_t(*)[8]>(&a[0]));
+      tmem_ld_x8(taddr + gc + 8, *reinterpret_cast<uint32_t(*)[8]>(&a[8]));
+      tmem_ld_x8(taddr + gc + G, *reinterpret_cast<uint32_t(*)[8]>(&b[0]));
+      tmem_ld_x8(taddr + gc + G + 8, *reinterpret_cast<uint32_t(*)[8]>(&b[8]));
+    } else {
+      tmem_ld_x8(taddr + oc, *reinterpret_cast<uint32_t(*)[8]>(&a[0]));
+      tmem_ld_x8(taddr + oc + 8, *reinterpret_cast<uint32_t(*)[8]>(&a[8]));
+    }
+    tmem_ld_wait();
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      T lo, hi;
+      if (SWIGLU) {
+        lo = epilogue_swiglu<T>(__uint_as_float(a[2 * j]), __uint_as_float(b[2 * j]));
+        hi = epilogue_swiglu<T>(__uint_as_float(a[2 * j + 1]), __uint_as_float(b[2 * j + 1]));
+      } else if (SCALE) {
+        lo = epilogue_scale<T>(__uint_as_float(a[2 * j]), sc);
+        hi = epilogue_scale<T>(__uint_as_float(a[2 * j + 1]), sc);
+      } else {
+        lo = Elem<T>::from_f(__uint_as_float(a[2 * j]));
+        hi = Elem<T>::from_f(__uint_as_float(a[2 * j + 1]));
+      }
+      o[j] = pack2<T>(lo, hi);
+    }
+    if (valid) {
+      *reinterpret_cast<uint4*>(dst + oc) = make_uint4(o[0], o[1], o[2], o[3]);
+      if (colbase + oc + 8 < Nout) *reinterpret_cast<uint4*>(dst + oc + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+template <typename T, int SH>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_constant__ KernelArgs args) {
-  using S = Shape<PAIR>;
+  using S = Shape<SH>;
+  constexpr bool STREAM = S::STREAM, PAIR = S::PAIR, DUO = S::DUO;
   constexpr int BN = S::BN, STAGES = S::STAGES, STAGE_BYTES = S::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -323,9 +408,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ int s_end[GM_MAX_E];
   __shared__ int s_rows[GM_MAX_E];        // rows per expert (all its ranges)
   __shared__ int s_tile_start[2][GM_MAX_E + 2];
-  __shared__ int s_map_row[2][GM_BM];     // per accumulator buffer: the tile's rows in A / C space
-  __shared__ int s_map_grp[2][GM_BM];     // ... and the range each row belongs to
-  __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (!PAIR SwiGLU)
+  __shared__ int s_map_row[2][GM_MAX_BN];  // per accumulator buffer: the tile's rows in A / C space
+  __shared__ int s_map_grp[2][GM_MAX_BN];  // ... and the range each row belongs to
+  __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (one-accumulator SwiGLU)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* stages =
@@ -334,33 +419,50 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   int* status = args.status;
   const int E = args.ranges, group_div = args.group_div, NP = args.n_problems;
   const int EL = E / group_div;  // experts; E counts row ranges
+  // DUO: the two CTAs of a cluster share every tile; `unit` numbers the clusters.
+  const int cr = DUO ? (int)cluster_ctarank() : 0;
+  const int unit = DUO ? (int)blockIdx.x >> 1 : (int)blockIdx.x;
+  const int units = DUO ? (int)gridDim.x >> 1 : (int)gridDim.x;
 
-  // per-problem tile geometry
-  auto cols_of = [&](int ph) {
-    return args.p[ph].swiglu ? (PAIR ? GM_BM : GM_BM / 2) : (PAIR ? 2 * GM_BM : GM_BM);
-  };
+  // per-problem tile geometry: output columns per tile, and the first weight row (= output
+  // column) this CTA loads for a tile (DUO: each CTA loads half of the tile's weight rows)
+  auto cols_of = [&](int ph) { return args.p[ph].swiglu ? (STREAM ? GM_BM / 2 : GM_BM) : (STREAM ? GM_BM : 2 * GM_BM); };
   auto col_blocks_of = [&](int ph) { return (args.p[ph].Nout + cols_of(ph) - 1) / cols_of(ph); };
   auto k_blocks_of = [&](int ph) { return (args.p[ph].K + S::BK - 1) / S::BK; };
+  auto colbase_of = [&](const Tile& tile) { return tile.cb * cols_of(tile.phase); };
+  auto wbase_of = [&](const Tile& tile) { return colbase_of(tile) + cr * (cols_of(tile.phase) >> 1); };
+
+  // the gather warps work only if some problem's token rows do not come by TMA
+  const bool gather_on = !(args.p[0].x_tma && (NP == 1 || args.p[1].x_tma));
 
   // Set-up that touches none of the kernel's inputs comes first, so that under programmatic
   // dependent launch it overlaps the tail of the previous kernel.
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1 + GM_GATHER_WARPS);
+      // the weights' expect_tx arrive plus one arrive per gather warp of the slot (both CTAs'
+      // in DUO, where only the leader's full barriers are used)
+      mbar_init(&full_bar[s], 1 + (gather_on ? S::CTAS * S::GATHER_GROUP : 0));
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], GM_EPI_WARPS);
+      mbar_init(&acc_empty[b], S::CTAS * GM_EPI_WARPS);  // DUO: the leader's, for both CTAs' epilogues
     }
     fence_barrier_init();
-    prefetch_tensormap(&args.p[0].map);
-    if (NP > 1) prefetch_tensormap(&args.p[1].map);
+    for (int ph = 0; ph < NP; ++ph) {
+      prefetch_tensormap(&args.p[ph].map);
+      if (args.p[ph].x_tma) prefetch_tensormap(&args.p[ph].xmap);
+    }
   }
   if (warp == 1) {
-    tmem_alloc(&s_tmem, S::TMEM_COLS);
-    tmem_relinquish();
+    if (DUO) {
+      tmem_alloc_pair(&s_tmem, S::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&s_tmem, S::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   pdl_wait();  // row ranges, activations, scale: all written by earlier kernels
   for (int i = threadIdx.x; i < E; i += GM_THREADS) {
@@ -396,10 +498,16 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (DUO) cluster_sync_all();  // the other CTA's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem = s_tmem;
+#ifdef SY_PROFILE
+  const long long prof_start = clock64();
+#endif
   const int tiles0 = s_tile_start[0][EL];
   const int total_tiles = tiles0 + (NP > 1 ? s_tile_start[1][EL] : 0);
+  // token rows of a STREAM tile's MMA: a multiple of 16
+  auto n_mma_of = [](int nvalid) { return max(16, (nvalid + 15) & ~15); };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -408,22 +516,55 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       bool alive = true;
       // streaming shape: an expert's weights are read once, so they are marked evict-first in L2
       const uint64_t policy = l2_policy_evict_first();
-      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && alive; t += units) {
         const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
         const Problem& P = args.p[tile.phase];
         const int Nfull = P.swiglu ? 2 * P.Nout : P.Nout;
-        const int y0 = tile.e * Nfull + tile.cb * cols_of(tile.phase);
+        const int y0 = tile.e * Nfull + wbase_of(tile);
         const int y1 = P.swiglu ? y0 + P.Nout : y0 + S::BOX_ROWS;
         const int k_blocks = k_blocks_of(tile.phase);
+        // contiguous token rows: the tile's first row in A (rows past the tile's end belong to the
+        // next expert or are zero-filled past A's end; their accumulator rows are never read)
+        const int xrow = s_begin[tile.e] + tile.row0 + cr * S::XR;
+        if (tile.phase == 1 && P.x_tma) {
+          // fused FFN: these rows are what the expert's gate/up tiles wrote. Wait (bounded) until
+          // all of them have been stored; they sit earlier in every block's tile list and their
+          // own loads are already in flight, so nothing here holds them up.
+          const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
+          if (ld_acquire_gpu(args.ready + tile.e) < need) {
+            const uint64_t start = global_timer_ns();
+            while (ld_acquire_gpu(args.ready + tile.e) < need) {
+              if (global_timer_ns() - start > GM_WAIT_NS) {
+                *status = DS_TIMEOUT_FLAG;
+                alive = false;
+                break;
+              }
+            }
+            if (!alive) break;
+          }
+          fence_proxy_async_all();  // they were written by plain stores; TMA reads them next
+        }
+        const uint32_t stage_bytes = S::W_BYTES + (P.x_tma ? S::X_BYTES : 0);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES, use = it / STAGES;
+          PROF_T0;
           if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS)) {
             *status = DS_TIMEOUT_EMPTY;
             alive = false;
             break;
           }
+          PROF_ADD(3);
           unsigned char* st = stages + (size_t)s * STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], S::W_BYTES);
+          if (DUO) {
+            // both CTAs' weight bytes are counted on the leader's barrier
+            if (cr == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * stage_bytes);
+            const uint32_t bar = cluster_map(&full_bar[s], 0);
+            tma_load_2d_pair(st, &P.map, kb * S::BK, y0, bar);
+            tma_load_2d_pair(st + S::BOX_ROWS * 128, &P.map, kb * S::BK, y1, bar);
+            if (P.x_tma) tma_load_2d_pair(st + S::W_BYTES, &P.xmap, kb * S::BK, xrow, bar);
+            continue;
+          }
+          mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
 #pragma unroll
           for (int a = 0; a < S::KATOMS; ++a) {
             const int kx = kb * S::BK + a * GM_ATOM_K;
@@ -434,147 +575,181 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
               tma_load_2d_hint(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s], policy);
               tma_load_2d_hint(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s], policy);
             }
+            if (P.x_tma) tma_load_2d(st + S::W_BYTES + a * S::X_ATOM_BYTES, &P.xmap, kx, xrow, &full_bar[s]);
           }
         }
       }
-      if (!alive)  // let the copies already issued land before the block can exit
+      if (!alive && cr == 0)  // let the copies already issued land before the block can exit
         for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j)
           mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // One thread. STREAM: weights are the M operand, token rows the N operand. PAIR / DUO: token
+    // rows are M and weight rows N (256 of them per instruction). DUO: the leader CTA's thread
+    // issues for both CTAs; its commits reach both CTAs' barriers.
+    if (lane == 0 && cr == 0) {
       const int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       const uint32_t ring_lo = umma_desc_lo(smem_u32(stages));
       int it = 0, cursor = 0, seen = 0, tile_no = 0;
       bool alive = true;
-      for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x, ++tile_no) {
+      for (int t = unit; t < total_tiles && alive; t += units, ++tile_no) {
         const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
         const int k_blocks = k_blocks_of(tile.phase);
         const int buf = tile_no & 1, use_t = tile_no >> 1;
+        PROF_T0;
         if (use_t > 0) {
-          if (!mbar_wait(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS)) {
+          const bool ok = DUO ? mbar_wait_cluster(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS)
+                              : mbar_wait(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS);
+          if (!ok) {
             *status = DS_TIMEOUT_TMEM;
             alive = false;
             break;
           }
           tc_fence_after_sync();
         }
-        const int n_mma = max(16, (tile.nvalid + 15) & ~15);
-        const uint32_t idesc = umma_idesc(fmt, GM_BM, n_mma);
-        const uint32_t d0 = tmem + buf * S::BUF_COLS, d1 = d0 + BN;
+        PROF_ADD(2);
+        const uint32_t idesc = umma_idesc(fmt, DUO ? 2 * GM_BM : GM_BM, STREAM ? n_mma_of(tile.nvalid) : 2 * GM_BM);
+        const uint32_t d = tmem + buf * S::BUF_COLS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, GM_WAIT_NS)) {
+          const bool ok = DUO ? mbar_wait_cluster(&full_bar[s], (it / STAGES) & 1, GM_WAIT_NS)
+                              : mbar_wait(&full_bar[s], (it / STAGES) & 1, GM_WAIT_NS);
+          if (!ok) {
             *status = DS_TIMEOUT_FULL;
             alive = false;
             break;
           }
           tc_fence_after_sync();
+          PROF_ADD(0);
           const uint32_t lo = ring_lo + s * (STAGE_BYTES >> 4);  // descriptor low word of the stage's first tile
 #pragma unroll
           for (int ks = 0; ks < S::BK / 16; ++ks) {
             const uint32_t accumulate = (kb | ks) != 0;
             const int atom = ks >> 2, within = (ks & 3) * 2;  // 32 bytes per 16 k inside the 128-byte atom
-            const uint32_t a_lo = lo + atom * (S::W_ATOM_BYTES >> 4) + within;
-            const uint32_t b_lo = lo + (S::W_BYTES >> 4) + atom * (S::X_ATOM_BYTES >> 4) + within;
-            umma_f16_lohi(d0, a_lo, b_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
-            if (PAIR) umma_f16_lohi(d1, a_lo + (S::BOX_ROWS * 128 >> 4), b_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
+            const uint32_t w_lo = lo + atom * (S::W_ATOM_BYTES >> 4) + within;
+            const uint32_t x_lo = lo + (S::W_BYTES >> 4) + atom * (S::X_ATOM_BYTES >> 4) + within;
+            if (DUO) umma_f16_lohi_pair(d, x_lo, w_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
+            else if (PAIR) umma_f16_lohi(d, x_lo, w_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
+            else umma_f16_lohi(d, w_lo, x_lo, UMMA_DESC_HI_K_SW128, idesc, accumulate);
           }
-          umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+          // the stage is free once these MMAs have read it
+          if (DUO) umma_commit_pair(&empty_bar[s], 3);
+          else umma_commit(&empty_bar[s]);
+          PROF_ADD(1);
         }
-        if (alive) umma_commit(&acc_full[buf]);
+        if (alive) {
+          if (DUO) umma_commit_pair(&acc_full[buf], 3);
+          else umma_commit(&acc_full[buf]);
+        }
       }
     }
   } else if (warp < 2 + GM_GATHER_WARPS) {
+    if (gather_on) {
     // ---------------------------------------------------------------- gather producers
-    // 16-byte asynchronous copies straight into the swizzled stage, DEPTH k blocks in flight
-    // per thread (commit groups), so that the L2 round trip of a gathered row is overlapped
-    // with the stages before it. A stage is published (proxy fence, then one arrive per warp)
-    // once the group that filled it has landed; filling runs ahead across tile boundaries.
-    constexpr int CHUNKS = S::BK / 8;                 // 16-byte chunks per token row per stage
-    constexpr int ROWS_PER_PASS = GM_GATHER_WARPS * 32 / CHUNKS;
-    constexpr int GI = BN / ROWS_PER_PASS;
-    constexpr int DEPTH = STAGES - 1;
-    const int g = threadIdx.x - 64;
-    const int c = g % CHUNKS, rsub = g / CHUNKS;      // chunk of the row; row within a pass
-    const int xoff = (c >> 3) * S::X_ATOM_BYTES;      // the atom the chunk belongs to
-    const int cc = c & 7;
-    int issued = 0, published = 0, cursor = 0, seen = 0;
+    // The tile's token rows, 16-byte asynchronous copies straight into the swizzled stage.
+    // Each slot of the ring has its own warps (GROUP of them, splitting the rows): they wait for
+    // the slot, issue the stage's copies, wait for them to land, make them visible to the tensor
+    // core (proxy fence) and arrive on the stage's barrier. Waiting for data therefore stalls
+    // only that slot's warps; the other slots fill meanwhile, and a stage is handed to the MMA
+    // issuer the moment it is complete. (A warp must see every use of its slot: an mbarrier
+    // parity wait tells the previous phase from the current one, not from older ones.)
+    // DUO: this CTA stages its half of the tile's rows and arrives on the leader's barrier.
+    constexpr int CHUNKS = S::BK / 8;            // 16-byte chunks per token row per stage
+    constexpr int RPI = 32 / CHUNKS;             // token rows one warp-wide copy instruction covers
+    constexpr int ITERS = S::XR / RPI;           // instructions per full stage (32 in every shape)
+    constexpr int OWN = S::XR / 32;              // row indices each lane keeps per tile
+    static_assert(ITERS == 32 && OWN * 32 == S::XR, "gather geometry");
+    constexpr int GROUP = S::GATHER_GROUP;       // warps per slot
+    const int gw = warp - 2;                     // 0..7
+    const int slot = gw % STAGES, part = gw / STAGES;  // part >= GROUP: a spare warp
+    const int c = lane % CHUNKS, sub = lane / CHUNKS;  // chunk of the row; row within an instruction
+    const int xatom = (c >> 3) * S::X_ATOM_BYTES, cc = c & 7;  // atom of the chunk; chunk within the 128-byte row
+    int it = 0, cursor = 0, seen = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+    for (int t = unit; t < total_tiles && alive; t += units) {
       const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
       const Problem& P = args.p[tile.phase];
       const int K = P.K, k_blocks = k_blocks_of(tile.phase);
-      if (tile.phase == 1) {
+      // which of this tile's stages land in this warp's slot
+      const int first_kb = (slot - it % STAGES + STAGES) % STAGES;
+      const int it0 = it;
+      it += k_blocks;
+      if (first_kb >= k_blocks || part >= GROUP) continue;
+      if (tile.phase == 1 && !P.x_tma) {
         // fused FFN: this tile reads what the expert's gate/up tiles wrote. Wait (bounded)
-        // until all of them have been stored; they sit earlier in every block's tile list.
-        const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0);
-        int ok = lane == 0 ? (ld_acquire_gpu(args.ready + tile.e) >= need) : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) {
-          // Not there yet. The gate/up tile it waits for may be this block's own, and that tile's
-          // last stages are filled but not yet published: publish everything first, then wait.
-          cp_async_wait<0>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          for (; published < issued; ++published)
-            if (lane == 0) mbar_arrive(&full_bar[published % STAGES]);
-          if (lane == 0) {
-            const uint64_t start = global_timer_ns();
-            while (ld_acquire_gpu(args.ready + tile.e) < need) {
-              if (global_timer_ns() - start > GM_WAIT_NS) {
-                *status = DS_TIMEOUT_FLAG;
-                break;
-              }
+        // until all of them have been stored; they sit earlier in every block's tile list, and
+        // everything this warp filled for them has already been handed over.
+        const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
+        int ok = 1;
+        if (lane == 0 && ld_acquire_gpu(args.ready + tile.e) < need) {
+          const uint64_t start = global_timer_ns();
+          while (ld_acquire_gpu(args.ready + tile.e) < need) {
+            if (global_timer_ns() - start > GM_WAIT_NS) {
+              *status = DS_TIMEOUT_FLAG;
+              ok = 0;
+              break;
             }
           }
-          __syncwarp();
         }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;  // one bounded wait per warp, not one per tile
       }
-      const T* A = static_cast<const T*>(P.A);
-      const T* src[GI];
+      // Row indices: lane l keeps those of the CTA's rows l, l + 32, ...; DUO: the second CTA
+      // stages the tile's rows from 128 on.
+      const int mine = min(max(tile.nvalid - cr * S::XR, 0), S::XR);  // valid rows this CTA stages
+      int own[OWN];
 #pragma unroll
-      for (int i = 0; i < GI; ++i) {
-        const int r = rsub + ROWS_PER_PASS * i;
-        src[i] = nullptr;
-        if (r < tile.nvalid) {
+      for (int j = 0; j < OWN; ++j) {
+        const int r = lane + 32 * j;
+        own[j] = 0;
+        if (r < mine) {
           int gr;
-          const int at = map_row(tile.e, tile.row0 + r, group_div, s_begin, s_end, gr);
-          const int row = P.a_rows ? P.a_rows[at] : at;
-          src[i] = A + (size_t)row * K + c * 8;
+          const int at = map_row(tile.e, tile.row0 + cr * S::XR + r, group_div, s_begin, s_end, gr);
+          own[j] = P.a_rows ? P.a_rows[at] : at;
         }
       }
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        const int s = issued % STAGES, use = issued / STAGES;
-        if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS)) {
-          *status = DS_TIMEOUT_EMPTY;
-          alive = false;
-          break;
+      const T* A = static_cast<const T*>(P.A) + c * 8;
+      const int iters = P.x_tma ? 0 : (mine + RPI - 1) / RPI;  // rows that come by TMA need no copies here
+      for (int kb = first_kb; kb < k_blocks; kb += STAGES) {
+        const int g = it0 + kb, s = g % STAGES, use = g / STAGES;
+        PROF_T0;
+        if (use > 0) {
+          int ok = lane == 0 ? (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS) : 1;
+          ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders the other lanes' copies after the wait
+          if (!ok) {
+            if (lane == 0) *status = DS_TIMEOUT_EMPTY;
+            alive = false;
+            break;
+          }
         }
-        unsigned char* x = stages + (size_t)s * STAGE_BYTES + S::W_BYTES + xoff;
-        const uint32_t bytes = kb * S::BK + c * 8 < K ? 16u : 0u;  // beyond K: zero fill
+        if (gw == 0 && lane == 0) PROF_ADD(5);
+        unsigned char* x = stages + (size_t)s * STAGE_BYTES + S::W_BYTES;
+        const bool in_k = kb * S::BK + c * 8 < K;  // beyond K: zero fill
+        const size_t koff = in_k ? (size_t)kb * S::BK : 0;
+        const uint32_t bytes = in_k ? 16u : 0u;
 #pragma unroll
-        for (int i = 0; i < GI; ++i) {
-          const int r = rsub + ROWS_PER_PASS * i;
-          if (src[i]) cp_async_16(x + r * 128 + ((cc ^ (r & 7)) << 4), bytes ? src[i] + (size_t)kb * S::BK : src[i], bytes);
+        for (int i0 = 0; i0 < ITERS; i0 += GROUP) {
+          const int i = i0 + part;
+          if (i < iters) {  // warp-uniform
+            const int r = i * RPI + sub;
+            // row r's index sits in lane r % 32, register r / 32 (= i * RPI / 32 for every lane)
+            const int row = __shfl_sync(0xffffffffu, own[(i0 * RPI) >> 5], r & 31);
+            if (r < mine) cp_async_16(x + xatom + r * 128 + ((cc ^ (r & 7)) << 4), A + (size_t)row * K + koff, bytes);
+          }
         }
         cp_async_commit();
-        ++issued;
-        if (issued - published > DEPTH) {
-          cp_async_wait<DEPTH>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[published % STAGES]);
-          ++published;
+        if (gw == 0 && lane == 0) PROF_ADD(6);
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (DUO) mbar_arrive_cluster(cluster_map(&full_bar[s], 0));
+          else mbar_arrive(&full_bar[s]);
         }
+        if (gw == 0 && lane == 0) PROF_ADD(7);
       }
     }
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    __syncwarp();
-    for (; published < issued; ++published)
-      if (lane == 0) mbar_arrive(&full_bar[published % STAGES]);
+    }  // gather_on
   } else {
     // ---------------------------------------------------------------- epilogue
     // A warp that gives up on a wait keeps walking the tiles (the barriers below must still
@@ -583,35 +758,54 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
     const int et = threadIdx.x - (2 + GM_GATHER_WARPS) * 32;  // 0..127 among the epilogue threads
     int cursor = 0, seen = 0, tile_no = 0, chunk_no = 0;
     bool alive = true;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_no) {
+    for (int t = unit; t < total_tiles; t += units, ++tile_no) {
       const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
       const Problem& P = args.p[tile.phase];
-      const int Nout = P.Nout, COLS = cols_of(tile.phase);
+      const int Nout = P.Nout, colbase = colbase_of(tile);
       const bool swiglu = P.swiglu != 0;
       const T* scale = static_cast<const T*>(P.scale);
       T* C = static_cast<T*>(P.C);
       const unsigned long long* c_table = P.c_table;
       const int buf = tile_no & 1, use_t = tile_no >> 1;
+      PROF_T0;
       if (alive && !mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
         *status = DS_TIMEOUT_MMA;
         alive = false;
       }
       tc_fence_after_sync();
-      if (swiglu)
-        epilogue_tile<T, PAIR, true, false>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, COLS, scale, C, c_table,
-                                            group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
-      else if (scale)
-        epilogue_tile<T, PAIR, false, true>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, COLS, scale, C, c_table,
-                                            group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
-      else
-        epilogue_tile<T, PAIR, false, false>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, COLS, scale, C, c_table,
-                                             group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
+      if (et == 0) PROF_ADD(8);
+      if constexpr (STREAM) {
+        if (swiglu)
+          epilogue_stream<T, true, false>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, colbase, scale, C, c_table,
+                                          group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
+        else if (scale)
+          epilogue_stream<T, false, true>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, colbase, scale, C, c_table,
+                                          group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
+        else
+          epilogue_stream<T, false, false>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, colbase, scale, C, c_table,
+                                           group_div, s_begin, s_end, s_map_row[buf], s_map_grp[buf], s_xch, out_tile);
+      } else {
+        if (swiglu)
+          epilogue_rows<T, SH, true, false>(tile, buf, tmem, q, lane, cr, alive, Nout, colbase, scale, C, c_table, group_div,
+                                            s_begin, s_end);
+        else if (scale)
+          epilogue_rows<T, SH, false, true>(tile, buf, tmem, q, lane, cr, alive, Nout, colbase, scale, C, c_table, group_div,
+                                            s_begin, s_end);
+        else
+          epilogue_rows<T, SH, false, false>(tile, buf, tmem, q, lane, cr, alive, Nout, colbase, scale, C, c_table, group_div,
+                                             s_begin, s_end);
+      }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0 && alive) mbar_arrive(&acc_empty[buf]);
+      if (et == 0) PROF_ADD(9);
+      if (lane == 0 && alive) {
+        if (DUO) mbar_arrive_cluster(cluster_map(&acc_empty[buf], 0));
+        else mbar_arrive(&acc_empty[buf]);
+      }
       if (NP > 1 && tile.phase == 0) {
         // fused FFN: publish this gate/up tile. All four warps' stores first (barrier), then
         // one thread makes them visible device-wide and counts the tile for its expert.
+        fence_proxy_async_all();  // the rows just stored may be read back by TMA
         named_barrier_sync(3, GM_EPI_WARPS * 32);
         if (et == 0) {
           __threadfence();
@@ -624,9 +818,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   // every role ends here; tensor memory goes back before the block exits
   tc_fence_before_sync();
   __syncthreads();
+#ifdef SY_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x < 2) atomicAdd(&g_prof[blockIdx.x * 16 + 10], (unsigned long long)(clock64() - prof_start));
+#endif
+  if (DUO) cluster_sync_all();  // neither CTA leaves while the other may still signal or read it
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, S::TMEM_COLS);
+    if (DUO) tmem_dealloc_pair(tmem, S::TMEM_COLS);
+    else tmem_dealloc(tmem, S::TMEM_COLS);
   }
   if (NP > 1 && threadIdx.x == 0) {
     // fused FFN: the last block out clears the per-expert counters for the next launch
@@ -675,6 +874,23 @@ static int weight_map(CUtensorMap* map, const void* B, uint64_t rows, uint64_t K
   return SY_OK;
 }
 
+// Tensor map over activations whose rows are the ranges' rows themselves, as a [rows, K]
+// matrix; box = box_rows x 64 k.
+static int activation_map(CUtensorMap* map, const void* A, uint64_t rows, uint64_t K, int dtype, int box_rows) {
+  EncodeTiledFn encode;
+  int rc = encode_fn(&encode);
+  if (rc != SY_OK) return rc;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {K * 2};
+  cuuint32_t box[2] = {GM_ATOM_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, dtype == SY_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                      2, const_cast<void*>(A), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SY_ERR_CUDA, "grouped kernel: cuTensorMapEncodeTiled (activations) failed (%d)", (int)r);
+  return SY_OK;
+}
+
 // One contraction as the entry points describe it.
 struct ProblemDesc {
   const void* A;
@@ -694,11 +910,12 @@ struct GroupedArgs {
   int ranges;              // number of row ranges (experts x ranges per expert)
   int group_div;           // ranges per expert: ranges [e*group_div, (e+1)*group_div) are expert e's rows
   int32_t* ready;          // fused FFN scratch: experts + 1 ints, zero before the first launch
+  int rows;                // upper bound of the row indices in begins / ends
   int dtype;
   cudaStream_t stream;
 };
 
-template <typename T, bool PAIR>
+template <typename T, int SH>
 static int launch_gemm(const GroupedArgs& a) {
   int sms = 0;
   int rc = device_sm_count(&sms);
@@ -711,8 +928,13 @@ static int launch_gemm(const GroupedArgs& a) {
   for (int i = 0; i < a.n_problems; ++i) {
     const ProblemDesc& d = a.p[i];
     rc = weight_map(&k.p[i].map, d.B, (uint64_t)experts * (d.swiglu ? 2 : 1) * d.n_out, (uint64_t)d.k_dim, a.dtype,
-                    Shape<PAIR>::BOX_ROWS);
+                    Shape<SH>::BOX_ROWS);
     if (rc != SY_OK) return rc;
+    k.p[i].x_tma = !d.a_rows && a.group_div == 1 && a.rows > 0;
+    if (k.p[i].x_tma) {
+      rc = activation_map(&k.p[i].xmap, d.A, (uint64_t)a.rows, (uint64_t)d.k_dim, a.dtype, Shape<SH>::XR);
+      if (rc != SY_OK) return rc;
+    }
     k.p[i].A = d.A;
     k.p[i].a_rows = d.a_rows;
     k.p[i].scale = d.scale;
@@ -728,19 +950,54 @@ static int launch_gemm(const GroupedArgs& a) {
   k.group_div = a.group_div;
   k.n_problems = a.n_problems;
   k.ready = a.ready;
-  auto kern = gemm_umma_kernel<T, PAIR>;
+  auto kern = gemm_umma_kernel<T, SH>;
+  // per device: 0 = not configured yet, else 1 + the number of CTA pairs that fit at once
   static std::atomic<int> configured[MAX_DEVICES];
   int dev = 0;
   SY_CUDA(cudaGetDevice(&dev));
-  if (!configured[dev].load(std::memory_order_acquire)) {
+  int state = configured[dev].load(std::memory_order_acquire);
+  if (!state) {
     SY_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
-    configured[dev].store(1, std::memory_order_release);
+    int pairs = 0;
+    if (SH == SH_DUO) {
+      // The grid is persistent and its blocks wait on one another (fused FFN), so it must not be
+      // larger than what is resident at once: ask how many clusters of two fit.
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(sms & ~1);
+      cfg.blockDim = dim3(GM_THREADS);
+      cfg.dynamicSmemBytes = GM_SMEM;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      SY_CUDA(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
+      if (pairs < 1) return fail(SY_ERR_CUDA, "grouped kernel: no cluster of two blocks fits on this device");
+      if (pairs > sms / 2) pairs = sms / 2;
+    }
+    state = 1 + pairs;
+    configured[dev].store(state, std::memory_order_release);
   }
+  if (SH == SH_DUO)
+    return launch_cluster_kernel(kern, 2, 2 * (state - 1), GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
   return launch_kernel(kern, sms, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
 }
 
+// Which compute tile a batch gets. Measured on a B200 at OLMoE sizes the CTA-pair tile is level
+// with the single-CTA tile (within 3% either way, 1024 rows per expert), so single CTAs are the
+// default; SY_GEMM_TILE=pair in the environment selects the pair tile. The two produce the same
+// bits (the same MMAs in the same k order).
+static int compute_shape_for(const GroupedArgs&, int) {
+  const char* v = getenv("SY_GEMM_TILE");
+  return v && v[0] == 'p' ? SH_DUO : SH_PAIR;
+}
+
 // Shared argument checks and dtype dispatch of the tensor-core entry points.
-int grouped_umma(bool pair, const char* name, const GroupedArgs& a, int rows) {
+int grouped_umma(bool pair, const char* name, const GroupedArgs& args, int rows) {
+  GroupedArgs a = args;
+  a.rows = rows;
   SY_REQUIRE(rows >= 0 && a.ranges >= 1 && a.ranges <= GM_MAX_E, "%s: 1..%d row ranges (got %d)", name, GM_MAX_E,
              a.ranges);
   SY_REQUIRE(a.group_div >= 1 && a.ranges % a.group_div == 0, "%s: %d ranges do not divide by %d", name, a.ranges,
@@ -761,8 +1018,14 @@ int grouped_umma(bool pair, const char* name, const GroupedArgs& a, int rows) {
                "%s: A, B and C must be 16-byte aligned", name);
   }
   SY_REQUIRE(a.n_problems == 1 || a.ready, "%s: the fused form needs its scratch", name);
-  if (a.dtype == SY_DTYPE_F16) return pair ? launch_gemm<__half, true>(a) : launch_gemm<__half, false>(a);
-  return pair ? launch_gemm<__nv_bfloat16, true>(a) : launch_gemm<__nv_bfloat16, false>(a);
+  const int shape = pair ? compute_shape_for(a, rows) : SH_STREAM;
+  if (a.dtype == SY_DTYPE_F16)
+    return shape == SH_DUO    ? launch_gemm<__half, SH_DUO>(a)
+           : shape == SH_PAIR ? launch_gemm<__half, SH_PAIR>(a)
+                              : launch_gemm<__half, SH_STREAM>(a);
+  return shape == SH_DUO    ? launch_gemm<__nv_bfloat16, SH_DUO>(a)
+         : shape == SH_PAIR ? launch_gemm<__nv_bfloat16, SH_PAIR>(a)
+                            : launch_gemm<__nv_bfloat16, SH_STREAM>(a);
 }
 
 static GroupedArgs single(const void* A, const int32_t* a_rows, const void* B, const int32_t* begins,
@@ -782,6 +1045,18 @@ static GroupedArgs single(const void* A, const int32_t* a_rows, const void* B, c
 }
 
 }  // namespace sy
+
+#ifdef SY_PROFILE
+extern "C" int sy_prof_read(unsigned long long* out, int reset) {
+  SY_CUDA(cudaDeviceSynchronize());
+  SY_CUDA(cudaMemcpyFromSymbol(out, sy::g_prof, sizeof(sy::g_prof)));
+  if (reset) {
+    unsigned long long zero[32] = {0};
+    SY_CUDA(cudaMemcpyToSymbol(sy::g_prof, zero, sizeof(zero)));
+  }
+  return SY_OK;
+}
+#endif
 
 extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,

@@ -287,7 +287,15 @@ def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_cou
     if mode == "gemv":
         return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 0)
     if mode in ("gemm", "cublas"):
-        return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 1)
+        # Compute-bound batches: bring the rows into expert order first (one streaming copy),
+        # so that both projections load their token tiles as contiguous TMA boxes. Gathering
+        # through a_rows inside the kernel is correct too (grouped_gemm does it, as in the
+        # reference) but cannot feed the tensor cores at this rate.
+        if a_rows is not None:
+            xs = torch.empty(rows, x.shape[1], dtype=x.dtype, device=x.device)
+            E.gather_rows(x, a_rows, xs)
+            x = xs
+        return E.expert_ffn(x, None, gate_up, down, offsets, rows, wsorted, 1)
     raise RuntimeError(f"ffn: unknown mode {mode!r}")
 
 

@@ -246,6 +246,33 @@ def test_fused_ffn_equals_the_two_grouped_calls(K, mode, N, skew):
         assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("N,skew,dtype", [(64, 0.0, torch.float16), (333, 2.0, torch.float16), (2048, 2.0, torch.float16),
+                                          (3000, 1.0, torch.bfloat16)])
+def test_compute_tiles_and_row_sources_agree_bit_for_bit(K, monkeypatch, N, skew, dtype):
+    """The compute shape has two tiles (one CTA; a CTA pair, SY_GEMM_TILE=pair) and two ways to
+    fetch token rows (gathered through a_rows; contiguous rows by TMA). All four combinations
+    run the same MMAs in the same k order: identical bits, separately and fused."""
+    h, router, gu, dn = cases.layer_inputs(N, skew=skew, dtype=dtype)
+    ridx, rw = mo.route_reference(h, router, 8, False)
+    counts, offsets, token, wsorted, pos_of = mo.sort_by_expert(ridx.int(), rw, 64)
+    hd, gud, dnd = h.to(DEV), gu.to(DEV), dn.to(DEV)
+    tok, off, ws = token.to(DEV), offsets.to(DEV), wsorted.to(DEV)
+    M = token.numel()
+    E = K.ext()
+    hs = hd[tok.long()].contiguous()
+    want_act = want = None
+    for tile in ("single", "pair"):
+        monkeypatch.setenv("SY_GEMM_TILE", tile)
+        for x, rows in ((hd, tok), (hs, None)):
+            act = E.grouped_gemm(x, rows, gud, off, None, 0, M, True, None)
+            y = E.grouped_gemm(act, None, dnd, off, None, 0, M, False, ws)
+            fused = E.expert_ffn(x, rows, gud, dnd, off, M, ws, 1)
+            if want is None:
+                want_act, want = act, y
+            assert torch.equal(act, want_act) and torch.equal(y, want) and torch.equal(fused, want)
+    assert E.device_status() == 0
+
+
 # ------------------------------------------------------------------------------ OLMoE shapes
 @pytest.fixture(scope="module")
 def olmoe():
