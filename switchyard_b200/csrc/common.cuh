@@ -119,7 +119,9 @@ template <typename T> __device__ __forceinline__ void unpack8(const uint4& v, fl
 // (linear -> silu -> mul -> linear -> mul): each intermediate is rounded to the 16-bit type.
 template <typename T> __device__ __forceinline__ T epilogue_swiglu(float acc_gate, float acc_up) {
   float g = round16<T>(acc_gate), u = round16<T>(acc_up);
-  float s = round16<T>(g / (1.f + expf(-g)));
+  // ex2.approx and the approximate divide are exact to about 2^-21: far inside the 16-bit
+  // rounding that follows, and several times cheaper than expf and an IEEE divide
+  float s = round16<T>(__fdividef(g, 1.f + __expf(-g)));
   return Elem<T>::from_f(s * u);
 }
 template <typename T> __device__ __forceinline__ T epilogue_scale(float acc, T scale) {
@@ -247,6 +249,13 @@ __device__ __forceinline__ bool elect_one() {
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(pred));
   return pred != 0;
+}
+
+// One 32-byte store (a whole sector) to a 32-byte aligned global address.
+__device__ __forceinline__ void st_global_32(void* p, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
+               "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
 }
 
 // ---- tcgen05 / tensor memory --------------------------------------------------------------
@@ -386,6 +395,15 @@ __device__ __forceinline__ void tmem_ld_x8(uint32_t addr, uint32_t (&r)[8]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(addr)
                : "memory");
+}
+// The same for 16 columns.
+__device__ __forceinline__ void tmem_ld_x16(uint32_t addr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr)
+      : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 

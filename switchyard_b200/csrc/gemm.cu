@@ -352,44 +352,55 @@ __device__ __forceinline__ void epilogue_rows(const Tile& tile, int buf, uint32_
   }
   // Accumulator columns: SwiGLU tiles hold [gate | up] groups of G columns (PAIR: one group of
   // 128 + 128; DUO: each CTA's weight rows are 64 + 64, so two groups); plain tiles hold the
-  // 256 output columns in order.
+  // 256 output columns in order. Sixteen output columns per step; the next step's accumulators
+  // are already on their way from tensor memory while this step's are turned into stores.
   constexpr int G = S::DUO ? 64 : 128;
   constexpr int OUT_COLS = SWIGLU ? 128 : 256;
-#pragma unroll 1
-  for (int oc = 0; oc < OUT_COLS; oc += 16) {
-    if (colbase + oc >= Nout) break;
-    uint32_t a[16], b[16];
+  const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31) == 0;  // this row's segments are 32-byte aligned
+  constexpr int STEPS = OUT_COLS / 16;
+  uint32_t a[2][16], b[2][16];
+  auto fetch = [&](int step, int slot) {
+    const int oc = step * 16;
     if (SWIGLU) {
       const int gc = (oc / G) * 2 * G + (oc % G);
-      tmem_ld_x8(taddr + gc, *reinterpret_cast<uint32_t(*)[8]>(&a[0]));
-      tmem_ld_x8(taddr + gc + 8, *reinterpret_cast<uint32_t(*)[8]>(&a[8]));
-      tmem_ld_x8(taddr + gc + G, *reinterpret_cast<uint32_t(*)[8]>(&b[0]));
-      tmem_ld_x8(taddr + gc + G + 8, *reinterpret_cast<uint32_t(*)[8]>(&b[8]));
+      tmem_ld_x16(taddr + gc, a[slot]);
+      tmem_ld_x16(taddr + gc + G, b[slot]);
     } else {
-      tmem_ld_x8(taddr + oc, *reinterpret_cast<uint32_t(*)[8]>(&a[0]));
-      tmem_ld_x8(taddr + oc + 8, *reinterpret_cast<uint32_t(*)[8]>(&a[8]));
+      tmem_ld_x16(taddr + oc, a[slot]);
     }
-    tmem_ld_wait();
+  };
+  fetch(0, 0);
+  tmem_ld_wait();
+#pragma unroll
+  for (int step = 0; step < STEPS; ++step) {
+    const int oc = step * 16, slot = step & 1;
+    if (colbase + oc >= Nout) break;  // warp-uniform
+    if (step + 1 < STEPS) fetch(step + 1, slot ^ 1);
     uint32_t o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       T lo, hi;
       if (SWIGLU) {
-        lo = epilogue_swiglu<T>(__uint_as_float(a[2 * j]), __uint_as_float(b[2 * j]));
-        hi = epilogue_swiglu<T>(__uint_as_float(a[2 * j + 1]), __uint_as_float(b[2 * j + 1]));
+        lo = epilogue_swiglu<T>(__uint_as_float(a[slot][2 * j]), __uint_as_float(b[slot][2 * j]));
+        hi = epilogue_swiglu<T>(__uint_as_float(a[slot][2 * j + 1]), __uint_as_float(b[slot][2 * j + 1]));
       } else if (SCALE) {
-        lo = epilogue_scale<T>(__uint_as_float(a[2 * j]), sc);
-        hi = epilogue_scale<T>(__uint_as_float(a[2 * j + 1]), sc);
+        lo = epilogue_scale<T>(__uint_as_float(a[slot][2 * j]), sc);
+        hi = epilogue_scale<T>(__uint_as_float(a[slot][2 * j + 1]), sc);
       } else {
-        lo = Elem<T>::from_f(__uint_as_float(a[2 * j]));
-        hi = Elem<T>::from_f(__uint_as_float(a[2 * j + 1]));
+        lo = Elem<T>::from_f(__uint_as_float(a[slot][2 * j]));
+        hi = Elem<T>::from_f(__uint_as_float(a[slot][2 * j + 1]));
       }
       o[j] = pack2<T>(lo, hi);
     }
     if (valid) {
-      *reinterpret_cast<uint4*>(dst + oc) = make_uint4(o[0], o[1], o[2], o[3]);
-      if (colbase + oc + 8 < Nout) *reinterpret_cast<uint4*>(dst + oc + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+      if (wide && colbase + oc + 16 <= Nout) {
+        st_global_32(dst + oc, o);  // a whole 32-byte sector per store
+      } else {
+        *reinterpret_cast<uint4*>(dst + oc) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (colbase + oc + 8 < Nout) *reinterpret_cast<uint4*>(dst + oc + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
     }
+    tmem_ld_wait();  // the next step's accumulators have arrived
   }
 }
 
@@ -404,6 +415,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
+#ifdef SY_PROFILE
+  __shared__ long long s_issue_clock[STAGES];
+#endif
   __shared__ int s_begin[GM_MAX_E];       // row ranges
   __shared__ int s_end[GM_MAX_E];
   __shared__ int s_rows[GM_MAX_E];        // rows per expert (all its ranges)
@@ -511,78 +525,86 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      int it = 0, cursor = 0, seen = 0;
-      bool alive = true;
-      // streaming shape: an expert's weights are read once, so they are marked evict-first in L2
-      const uint64_t policy = l2_policy_evict_first();
-      for (int t = unit; t < total_tiles && alive; t += units) {
-        const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
-        const Problem& P = args.p[tile.phase];
-        const int Nfull = P.swiglu ? 2 * P.Nout : P.Nout;
-        const int y0 = tile.e * Nfull + wbase_of(tile);
-        const int y1 = P.swiglu ? y0 + P.Nout : y0 + S::BOX_ROWS;
-        const int k_blocks = k_blocks_of(tile.phase);
-        // contiguous token rows: the tile's first row in A (rows past the tile's end belong to the
-        // next expert or are zero-filled past A's end; their accumulator rows are never read)
-        const int xrow = s_begin[tile.e] + tile.row0 + cr * S::XR;
-        if (tile.phase == 1 && P.x_tma) {
-          // fused FFN: these rows are what the expert's gate/up tiles wrote. Wait (bounded) until
-          // all of them have been stored; they sit earlier in every block's tile list and their
-          // own loads are already in flight, so nothing here holds them up.
-          const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
-          if (ld_acquire_gpu(args.ready + tile.e) < need) {
-            const uint64_t start = global_timer_ns();
-            while (ld_acquire_gpu(args.ready + tile.e) < need) {
-              if (global_timer_ns() - start > GM_WAIT_NS) {
-                *status = DS_TIMEOUT_FLAG;
-                alive = false;
-                break;
-              }
+    // The whole warp walks the tiles; lane 0 waits for the slot and announces the stage's bytes,
+    // then each box of the stage is issued by its own lane (issuing a TMA load keeps a thread
+    // busy for about a hundred clocks; three to six boxes in a row would make this thread the
+    // bottleneck of the ring).
+    int it = 0, cursor = 0, seen = 0;
+    bool alive = true;
+    // streaming shape: an expert's weights are read once, so they are marked evict-first in L2
+    const uint64_t policy = l2_policy_evict_first();
+    for (int t = unit; t < total_tiles && alive; t += units) {
+      const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
+      const Problem& P = args.p[tile.phase];
+      const int Nfull = P.swiglu ? 2 * P.Nout : P.Nout;
+      const int y0 = tile.e * Nfull + wbase_of(tile);
+      const int y1 = P.swiglu ? y0 + P.Nout : y0 + S::BOX_ROWS;
+      const int k_blocks = k_blocks_of(tile.phase);
+      // contiguous token rows: the tile's first row in A (rows past the tile's end belong to the
+      // next expert or are zero-filled past A's end; their accumulator rows are never read)
+      const int xrow = s_begin[tile.e] + tile.row0 + cr * S::XR;
+      if (tile.phase == 1 && P.x_tma) {
+        // fused FFN: these rows are what the expert's gate/up tiles wrote. Wait (bounded) until
+        // all of them have been stored; they sit earlier in every block's tile list and their
+        // own loads are already in flight, so nothing here holds them up.
+        const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
+        int ok = 1;
+        if (lane == 0 && ld_acquire_gpu(args.ready + tile.e) < need) {
+          const uint64_t start = global_timer_ns();
+          while (ld_acquire_gpu(args.ready + tile.e) < need) {
+            if (global_timer_ns() - start > GM_WAIT_NS) {
+              *status = DS_TIMEOUT_FLAG;
+              ok = 0;
+              break;
             }
-            if (!alive) break;
-          }
-          fence_proxy_async_all();  // they were written by plain stores; TMA reads them next
-        }
-        const uint32_t stage_bytes = S::W_BYTES + (P.x_tma ? S::X_BYTES : 0);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES, use = it / STAGES;
-          PROF_T0;
-          if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS)) {
-            *status = DS_TIMEOUT_EMPTY;
-            alive = false;
-            break;
-          }
-          PROF_ADD(3);
-          unsigned char* st = stages + (size_t)s * STAGE_BYTES;
-          if (DUO) {
-            // both CTAs' weight bytes are counted on the leader's barrier
-            if (cr == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * stage_bytes);
-            const uint32_t bar = cluster_map(&full_bar[s], 0);
-            tma_load_2d_pair(st, &P.map, kb * S::BK, y0, bar);
-            tma_load_2d_pair(st + S::BOX_ROWS * 128, &P.map, kb * S::BK, y1, bar);
-            if (P.x_tma) tma_load_2d_pair(st + S::W_BYTES, &P.xmap, kb * S::BK, xrow, bar);
-            continue;
-          }
-          mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
-#pragma unroll
-          for (int a = 0; a < S::KATOMS; ++a) {
-            const int kx = kb * S::BK + a * GM_ATOM_K;
-            if (PAIR) {
-              tma_load_2d(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s]);
-              tma_load_2d(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s]);
-            } else {
-              tma_load_2d_hint(st + a * S::W_ATOM_BYTES, &P.map, kx, y0, &full_bar[s], policy);
-              tma_load_2d_hint(st + a * S::W_ATOM_BYTES + S::BOX_ROWS * 128, &P.map, kx, y1, &full_bar[s], policy);
-            }
-            if (P.x_tma) tma_load_2d(st + S::W_BYTES + a * S::X_ATOM_BYTES, &P.xmap, kx, xrow, &full_bar[s]);
           }
         }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) {
+          alive = false;
+          break;
+        }
+        fence_proxy_async_all();  // they were written by plain stores; TMA reads them next
       }
-      if (!alive && cr == 0)  // let the copies already issued land before the block can exit
-        for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j)
-          mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
+      const uint32_t stage_bytes = S::W_BYTES + (P.x_tma ? S::X_BYTES : 0);
+      // this lane's box within a stage: atom a = lane / 3; kind 0, 1 = the two weight boxes, 2 = token rows
+      const int atom = lane / 3, kind = lane % 3;
+      const bool has_box = atom < S::KATOMS && (kind < 2 || P.x_tma);
+      const void* map = kind < 2 ? static_cast<const void*>(&P.map) : static_cast<const void*>(&P.xmap);
+      const int by = kind == 0 ? y0 : kind == 1 ? y1 : xrow;
+      const int boff = kind == 0   ? atom * S::W_ATOM_BYTES
+                       : kind == 1 ? atom * S::W_ATOM_BYTES + S::BOX_ROWS * 128
+                                   : S::W_BYTES + atom * S::X_ATOM_BYTES;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % STAGES, use = it / STAGES;
+        PROF_T0;
+        int ok = 1;
+        if (lane == 0) {
+          if (use > 0) ok = (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS);
+          // DUO: both CTAs' bytes are counted on the leader's barrier
+          if (ok && cr == 0) mbar_arrive_expect_tx(&full_bar[s], S::CTAS * stage_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders the other lanes' loads after the wait
+        if (!ok) {
+          if (lane == 0) *status = DS_TIMEOUT_EMPTY;
+          alive = false;
+          break;
+        }
+        if (lane == 0) PROF_ADD(3);
+#ifdef SY_PROFILE
+        if (lane == 0) s_issue_clock[s] = clock64();
+#endif
+        if (has_box) {
+          unsigned char* dst = stages + (size_t)s * STAGE_BYTES + boff;
+          const int kx = kb * S::BK + atom * GM_ATOM_K;
+          if (DUO) tma_load_2d_pair(dst, map, kx, by, cluster_map(&full_bar[s], 0));
+          else if (STREAM && kind < 2) tma_load_2d_hint(dst, map, kx, by, &full_bar[s], policy);
+          else tma_load_2d(dst, map, kx, by, &full_bar[s]);
+        }
+        if (lane == 0) PROF_ADD(4);
+      }
     }
+    if (!alive && cr == 0 && lane == 0)  // let the copies already issued land before the block can exit
+      for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     // One thread. STREAM: weights are the M operand, token rows the N operand. PAIR / DUO: token
@@ -622,6 +644,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           }
           tc_fence_after_sync();
           PROF_ADD(0);
+#ifdef SY_PROFILE
+          if (blockIdx.x < 2) {  // slot 11: clocks from a stage's issue to its use; slot 12: stages
+            atomicAdd(&g_prof[blockIdx.x * 16 + 11], (unsigned long long)(clock64() - s_issue_clock[s]));
+            atomicAdd(&g_prof[blockIdx.x * 16 + 12], 1ull);
+          }
+#endif
           const uint32_t lo = ring_lo + s * (STAGE_BYTES >> 4);  // descriptor low word of the stage's first tile
 #pragma unroll
           for (int ks = 0; ks < S::BK / 16; ++ks) {
