@@ -38,6 +38,9 @@ sys.path.insert(0, ROOT)
 SWEEP = (1, 8, 32, 64)
 H, I, E, TOPK = 2048, 1024, 64, 8
 EXPERT_BYTES = 3 * H * I * 2          # fp16 bytes of one expert's weights
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused expert-FFN launch at T=64 (all 64 experts
+# used) from the ncu capture summarised in profiles/expert_ffn_decode_T64_fp16.md
+NCU_TRAFFIC_BYTES = 805.65e6 + 4.94e6
 LAYERS = 8                             # resident weight sets used in rotation (8 x 805 MB)
 METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
 
@@ -279,17 +282,19 @@ def run_single_gpu(args):
             idx, w = kernels.route(hs[T], router, TOPK, False)
             counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, E)
             sorted_in.append((token, offsets, wsorted))
-        for rep in range(max(args.steps, 8) + 3):
-            l = rep % LAYERS
-            token, offsets, wsorted = sorted_in[l]
+        # One pair of events around a full rotation of back-to-back launches: with a single launch
+        # between the events the host's launch latency (about 10 us) would be counted as kernel time.
+        for rep in range(max(args.steps // 2, 4) + 2):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            ext.expert_ffn(hs[T], token, layers[l][1], layers[l][2], offsets, T * TOPK, wsorted, 0)
+            for l in range(LAYERS):
+                token, offsets, wsorted = sorted_in[l]
+                ext.expert_ffn(hs[T], token, layers[l][1], layers[l][2], offsets, T * TOPK, wsorted, 0)
             b.record(stream)
             stream.synchronize()
-            if rep >= 3:
-                kern_ms.append(a.elapsed_time(b))
-                kern_bytes.append(used[(T, l)] * EXPERT_BYTES)
+            if rep >= 2:
+                kern_ms.append(a.elapsed_time(b) / LAYERS)
+                kern_bytes.append(sum(used[(T, l)] for l in range(LAYERS)) * EXPERT_BYTES / LAYERS)
     peak, peak_src = peaks()
     achieved = sum(kern_bytes) / (sum(kern_ms) / 1e3) / 1e9
     assert ext.device_status(dev) == 0
@@ -316,7 +321,7 @@ def run_single_gpu(args):
                 "api": "switchyard_b200.kernels.moe_layer, eager, host buffers pinned"},
         "gpu_launches": args.steps * len(SWEEP) * 4,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, streaming shape>, fused FFN (sy_expert_ffn)",
+                     "traffic": NCU_TRAFFIC_BYTES, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, streaming shape>, fused FFN (sy_expert_ffn)",
                      "workload": "T=64, gate/up + down projections of one layer in one launch, weight sets in rotation",
                      "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
                      "vs_nominal_8TBps": achieved / 8000.0},

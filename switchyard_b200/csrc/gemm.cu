@@ -543,10 +543,51 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       // contiguous token rows: the tile's first row in A (rows past the tile's end belong to the
       // next expert or are zero-filled past A's end; their accumulator rows are never read)
       const int xrow = s_begin[tile.e] + tile.row0 + cr * S::XR;
+      const uint32_t stage_bytes = S::W_BYTES + (P.x_tma ? S::X_BYTES : 0);
+      // this lane's box within a stage: atom a = lane / 3; kind 0, 1 = the two weight boxes, 2 = token rows
+      const int atom = lane / 3, kind = lane % 3;
+      const bool has_box = atom < S::KATOMS && (kind < 2 || P.x_tma);
+      const void* map = kind < 2 ? static_cast<const void*>(&P.map) : static_cast<const void*>(&P.xmap);
+      const int by = kind == 0 ? y0 : kind == 1 ? y1 : xrow;
+      const int boff = kind == 0   ? atom * S::W_ATOM_BYTES
+                       : kind == 1 ? atom * S::W_ATOM_BYTES + S::BOX_ROWS * 128
+                                   : S::W_BYTES + atom * S::X_ATOM_BYTES;
+      // One stage: lane 0 waits for the slot and announces the bytes, then every box is issued by
+      // its lane.
+      auto issue_stage = [&](int kb, int g) -> bool {
+        const int s = g % STAGES, use = g / STAGES;
+        PROF_T0;
+        int ok = 1;
+        if (lane == 0) {
+          if (use > 0) ok = (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS);
+          // DUO: both CTAs' bytes are counted on the leader's barrier
+          if (ok && cr == 0) mbar_arrive_expect_tx(&full_bar[s], S::CTAS * stage_bytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders the other lanes' loads after the wait
+        if (!ok) {
+          if (lane == 0) *status = DS_TIMEOUT_EMPTY;
+          return false;
+        }
+        if (lane == 0) PROF_ADD(3);
+#ifdef SY_PROFILE
+        if (lane == 0) s_issue_clock[s] = clock64();
+#endif
+        if (has_box) {
+          unsigned char* dst = stages + (size_t)s * STAGE_BYTES + boff;
+          const int kx = kb * S::BK + atom * GM_ATOM_K;
+          if (DUO) tma_load_2d_pair(dst, map, kx, by, cluster_map(&full_bar[s], 0));
+          else if (STREAM && kind < 2) tma_load_2d_hint(dst, map, kx, by, &full_bar[s], policy);
+          else tma_load_2d(dst, map, kx, by, &full_bar[s]);
+        }
+        if (lane == 0) PROF_ADD(4);
+        return true;
+      };
       if (tile.phase == 1 && P.x_tma) {
-        // fused FFN: these rows are what the expert's gate/up tiles wrote. Wait (bounded) until
-        // all of them have been stored; they sit earlier in every block's tile list and their
-        // own loads are already in flight, so nothing here holds them up.
+        // fused FFN: the token rows are what the expert's gate/up tiles wrote. Wait (bounded) until
+        // all of them have been stored; they sit earlier in every block's tile list and their own
+        // loads are already in flight, so nothing here holds them up. (Sending this tile's weight
+        // boxes ahead of the wait was measured: it takes bandwidth from the gate/up tiles that the
+        // wait is for, and the layer got 6% slower at 64 tokens.)
         const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
         int ok = 1;
         if (lane == 0 && ld_acquire_gpu(args.ready + tile.e) < need) {
@@ -565,43 +606,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
         }
         fence_proxy_async_all();  // they were written by plain stores; TMA reads them next
       }
-      const uint32_t stage_bytes = S::W_BYTES + (P.x_tma ? S::X_BYTES : 0);
-      // this lane's box within a stage: atom a = lane / 3; kind 0, 1 = the two weight boxes, 2 = token rows
-      const int atom = lane / 3, kind = lane % 3;
-      const bool has_box = atom < S::KATOMS && (kind < 2 || P.x_tma);
-      const void* map = kind < 2 ? static_cast<const void*>(&P.map) : static_cast<const void*>(&P.xmap);
-      const int by = kind == 0 ? y0 : kind == 1 ? y1 : xrow;
-      const int boff = kind == 0   ? atom * S::W_ATOM_BYTES
-                       : kind == 1 ? atom * S::W_ATOM_BYTES + S::BOX_ROWS * 128
-                                   : S::W_BYTES + atom * S::X_ATOM_BYTES;
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-        const int s = it % STAGES, use = it / STAGES;
-        PROF_T0;
-        int ok = 1;
-        if (lane == 0) {
-          if (use > 0) ok = (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS);
-          // DUO: both CTAs' bytes are counted on the leader's barrier
-          if (ok && cr == 0) mbar_arrive_expect_tx(&full_bar[s], S::CTAS * stage_bytes);
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders the other lanes' loads after the wait
-        if (!ok) {
-          if (lane == 0) *status = DS_TIMEOUT_EMPTY;
-          alive = false;
-          break;
-        }
-        if (lane == 0) PROF_ADD(3);
-#ifdef SY_PROFILE
-        if (lane == 0) s_issue_clock[s] = clock64();
-#endif
-        if (has_box) {
-          unsigned char* dst = stages + (size_t)s * STAGE_BYTES + boff;
-          const int kx = kb * S::BK + atom * GM_ATOM_K;
-          if (DUO) tma_load_2d_pair(dst, map, kx, by, cluster_map(&full_bar[s], 0));
-          else if (STREAM && kind < 2) tma_load_2d_hint(dst, map, kx, by, &full_bar[s], policy);
-          else tma_load_2d(dst, map, kx, by, &full_bar[s]);
-        }
-        if (lane == 0) PROF_ADD(4);
-      }
+      for (int kb = 0; kb < k_blocks && alive; ++kb, ++it) alive = issue_stage(kb, it);
     }
     if (!alive && cr == 0 && lane == 0)  // let the copies already issued land before the block can exit
       for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
