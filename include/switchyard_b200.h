@@ -115,9 +115,13 @@ int sy_grouped_gemv(const void* A, const int32_t* a_rows, const void* B, const i
 /* grouped_gemm — replaces `grouped_gemm` (moe_kernels.cu:264-298, kernel l.159-261) and the
  * host-side `tile_offsets` / `total_tiles` arguments, which this implementation does not need:
  * tiles are scheduled on the device from `offsets`. Same contract as sy_grouped_gemv; the same
- * kernel in its compute-bound shape: 128 token rows per tile against two 128-row weight tiles
- * (gate and up of the same columns with swiglu) in two tensor-memory accumulators, rows
- * gathered from A in-kernel, epilogues fused. */
+ * kernel in its compute-bound shape: 128 token rows (the MMA's M operand) against 256 weight
+ * rows (with swiglu 128 gate + 128 up rows of the same columns) per tile, one accumulator of
+ * 256 tensor-memory columns, epilogues fused. With a_rows == NULL the token rows of a tile are
+ * contiguous in A and arrive as TMA boxes; with a_rows they are gathered in-kernel with 16-byte
+ * copies, which is about 30 % slower at large batches: sort the rows first (sy_gather_rows) when
+ * the batch is compute-bound. A then needs at least `rows` rows.
+ * The bits of the two modes (gemv / gemm) may differ from each other, as in the reference. */
 int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                     int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                     int dtype, void* stream);
