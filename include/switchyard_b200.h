@@ -165,6 +165,7 @@ int sy_gather_rows(const void* src, const int32_t* index, int n, int row_bytes, 
  * two device buffers (same GPU or peers) on `stream`. */
 int sy_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 
+
 /* enable_peer_access — replaces `enable_peer_access` (moe_kernels.cu:477-489). Sets
  * *enabled_out to 1 if `device` can (now) address `peer`'s memory, 0 if the hardware cannot.
  * Already-enabled is not an error. */
@@ -220,6 +221,27 @@ int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t* epoch_cou
 
 /* ep_wait — waits (bounded, 2 s) until flags[i] >= *epoch_counter for i < n (n <= 32). */
 int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, void* stream);
+
+/* ep_dispatch_build — sy_ep_dispatch and sy_ep_wait_build in ONE launch: the dispatch's last
+ * block, once it has published this rank's rows, waits (bounded) for every sender's arrival flag
+ * and writes the row groups and the result table. Arguments: those of sy_ep_dispatch, then
+ * those of sy_ep_wait_build (arrive_flags, meta, y_dst, out_row_bytes, begins, ends, c_table).
+ * Replaces the same reference lines as the two (switchyard/ep.py:193-223, 239-262). */
+int sy_ep_dispatch_build(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
+                         int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
+                         void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* done_counter,
+                         int32_t* epoch_counter, const int32_t* arrive_flags, const int32_t* meta, void* const* y_dst,
+                         int out_row_bytes, int32_t* begins, int32_t* ends, uint64_t* c_table, void* stream);
+
+/* ep_combine — sy_ep_signal, sy_ep_wait and sy_combine in ONE launch: block 0 release-stores the
+ * layer's epoch into every sender's return flag (flag_dst), every block waits (bounded) until
+ * all n_ranks owners have done the same for this rank (ret_flags), then sums its token's rows as
+ * sy_combine does (same order, same bits; y is read with L1 bypassed, its rows were stored by
+ * other GPUs while the kernel waited). A rank with n_tokens == 0 still launches one block.
+ * Replaces switchyard/ep.py:264-272 followed by the combine (moe_kernels.cu:417-444). */
+int sy_ep_combine(int32_t* const* flag_dst, const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter,
+                  const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out,
+                  int dtype, void* stream);
 
 /* ipc_export / ipc_open / ipc_close — map one rank's window into another process (CUDA IPC).
  * export: 64-byte handle of the allocation containing ptr and ptr's offset in it.

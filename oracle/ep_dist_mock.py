@@ -158,6 +158,28 @@ class _Lib:
         return rc or self.sy_grouped_segments(act, down, begins, ends, n_ranges, per_expert, rows_bound, hidden, inter, 0,
                                               wsorted, y, y_table, dtype, compute_shape, stream)
 
+    def sy_ep_dispatch_build(self, h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
+                             done_counter, epoch_counter, arrive_flags, meta, y_dst, out_row_bytes, begins, ends, c_table,
+                             stream):
+        rc = self.sy_ep_dispatch(h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
+                                 done_counter, epoch_counter, stream)
+        return rc or self.sy_ep_wait_build(arrive_flags, meta, per, R, cap, y_dst, out_row_bytes, epoch_counter, begins,
+                                           ends, c_table, stream)
+
+    def sy_ep_combine(self, flag_dst, ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, out, dtype,
+                      stream):
+        rc = self.sy_ep_signal(flag_dst, R, epoch_counter, stream) or self.sy_ep_wait(ret_flags, R, epoch_counter, stream)
+        if rc or n_tokens == 0:
+            return rc
+        dt = torch.float16 if dtype == 0 else torch.bfloat16
+        m = n_tokens * top_k
+        pos = torch.from_numpy(_view(pos_of, m, np.int32).copy())
+        ix = torch.from_numpy(_view(idx, m, np.int32).copy()).view(n_tokens, top_k)
+        rows = int(pos.max()) + 1
+        yy = _torch16(_addr(y), rows, hidden, dt)
+        _torch16(_addr(out), n_tokens, hidden, dt).copy_(mo.combine_expert_order(yy, pos, ix, n_tokens))
+        return 0
+
     def sy_ep_signal(self, flag_dst, R, epoch_counter, stream):
         epoch = int(_view(epoch_counter, 1, np.int32)[0])
         for s in range(R):

@@ -48,6 +48,11 @@ SYMBOLS = {
                                  c_void_p, c_void_p]),
     "sy_ep_signal": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
     "sy_ep_wait": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+    "sy_ep_dispatch_build": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_void_p]),
+    "sy_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p, c_int, c_void_p]),
     "sy_ipc_export": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
     "sy_ipc_open": (c_int, [c_void_p, ctypes.c_uint64, ctypes.POINTER(c_void_p)]),
     "sy_ipc_close": (c_int, [c_void_p, ctypes.c_uint64]),

@@ -68,7 +68,10 @@ constexpr int GM_GATHER_WARPS = 8;
 constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_GATHER_WARPS + GM_EPI_WARPS) * 32;
 constexpr int GM_MAX_E = 256;
-constexpr int GM_RING_BYTES = 192 * 1024;          // shared-memory ring of stages
+#ifndef SY_RING_KB
+#define SY_RING_KB 192
+#endif
+constexpr int GM_RING_BYTES = SY_RING_KB * 1024;   // shared-memory ring of stages
 constexpr int GM_MAX_BN = 256;                      // most token rows in a tile (any shape)
 constexpr int GM_EPI_ROWS = 64;                    // token rows the epilogue stages per pass
 constexpr int GM_EPI_BYTES = GM_EPI_ROWS * GM_BM * 2;  // staged output tile: 64 rows x 128 columns
@@ -87,7 +90,7 @@ constexpr uint64_t GM_WAIT_NS = 1000000000ull;
 //   SH_DUO   (mode "gemm", many rows per expert): two CTAs on neighbouring SMs work as one
 //            (tcgen05 cta_group::2). A tile is 256 token rows (128 gathered by each CTA) by 256
 //            weight rows (128 loaded by each CTA); the pair's MMAs read both halves. Per MMA a
-//            CTA fills 2/3 of the shared memory a PAIR tile needs. 32 KB stages x 6.
+//            CTA fills 2/3 of the shared memory a PAIR tile needs. 128 k per stage: 64 KB stages x 3.
 enum { SH_STREAM = 0, SH_PAIR = 1, SH_DUO = 2 };
 template <int SH> struct Shape {
   static constexpr bool STREAM = SH == SH_STREAM, PAIR = SH == SH_PAIR, DUO = SH == SH_DUO;
@@ -95,13 +98,13 @@ template <int SH> struct Shape {
   static constexpr int XR = STREAM ? 64 : 128;              // token rows one CTA stages
   static constexpr int WR = PAIR ? 256 : 128;               // weight rows one CTA stages
   static constexpr int BOX_ROWS = WR / 2;                   // weight rows per TMA box (two boxes per atom)
-  static constexpr int KATOMS = STREAM ? 2 : 1;             // 64-wide k atoms per stage
+  static constexpr int KATOMS = PAIR ? 1 : 2;               // 64-wide k atoms per stage
   static constexpr int BK = KATOMS * GM_ATOM_K;             // k per stage
   static constexpr int W_ATOM_BYTES = WR * 128;             // weight bytes of one atom (both boxes)
   static constexpr int X_ATOM_BYTES = XR * 128;
   static constexpr int W_BYTES = KATOMS * W_ATOM_BYTES;     // weight bytes per stage
   static constexpr int X_BYTES = KATOMS * X_ATOM_BYTES;
-  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;     // 48 KB, or 32 KB for DUO
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;     // 48 KB, or 64 KB for DUO
   static constexpr int STAGES = GM_RING_BYTES / STAGE_BYTES;
   static constexpr int BUF_COLS = STREAM ? BN : 256;        // tensor-memory columns per accumulator buffer
   static constexpr int TMEM_COLS = 2 * BUF_COLS;            // two buffers: 128 or 512
@@ -690,9 +693,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
     // DUO: this CTA stages its half of the tile's rows and arrives on the leader's barrier.
     constexpr int CHUNKS = S::BK / 8;            // 16-byte chunks per token row per stage
     constexpr int RPI = 32 / CHUNKS;             // token rows one warp-wide copy instruction covers
-    constexpr int ITERS = S::XR / RPI;           // instructions per full stage (32 in every shape)
+    constexpr int ITERS = S::XR / RPI;           // instructions per full stage
     constexpr int OWN = S::XR / 32;              // row indices each lane keeps per tile
-    static_assert(ITERS == 32 && OWN * 32 == S::XR, "gather geometry");
+    static_assert(ITERS * RPI == S::XR && OWN * 32 == S::XR && 32 % (S::GATHER_GROUP * RPI) == 0, "gather geometry");
     constexpr int GROUP = S::GATHER_GROUP;       // warps per slot
     const int gw = warp - 2;                     // 0..7
     const int slot = gw % STAGES, part = gw / STAGES;  // part >= GROUP: a spare warp
@@ -1018,13 +1021,21 @@ static int launch_gemm(const GroupedArgs& a) {
   return launch_kernel(kern, sms, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
 }
 
-// Which compute tile a batch gets. Measured on a B200 at OLMoE sizes the CTA-pair tile is level
-// with the single-CTA tile (within 3% either way, 1024 rows per expert), so single CTAs are the
-// default; SY_GEMM_TILE=pair in the environment selects the pair tile. The two produce the same
-// bits (the same MMAs in the same k order).
-static int compute_shape_for(const GroupedArgs&, int) {
+// Which compute tile a batch gets. Measured on a B200 at OLMoE sizes, whole layer, Zipf-skewed
+// routing: the CTA-pair tile (256 token rows) wins by 3 % at 1024 rows per expert on average and
+// loses 1-6 % at 512 and 128, where more of its rows are padding; uniform routing moves the
+// crossover down, and the fused kernel alone gains up to 8 %. So: CTA pairs from 768 rows per
+// expert on average, for plain sorted batches (one range per expert, contiguous rows);
+// SY_GEMM_TILE=single|pair in the environment forces one. The two produce the same bits (the
+// same MMAs in the same k order).
+constexpr int GM_DUO_MIN_MEAN_ROWS = 768;
+static int compute_shape_for(const GroupedArgs& a, int rows) {
   const char* v = getenv("SY_GEMM_TILE");
-  return v && v[0] == 'p' ? SH_DUO : SH_PAIR;
+  if (v && v[0] == 's') return SH_PAIR;
+  if (v && v[0] == 'p') return SH_DUO;
+  bool plain = a.group_div == 1;
+  for (int i = 0; i < a.n_problems; ++i) plain = plain && !a.p[i].a_rows && !a.p[i].c_table;
+  return plain && rows >= a.ranges * GM_DUO_MIN_MEAN_ROWS ? SH_DUO : SH_PAIR;
 }
 
 // Shared argument checks and dtype dispatch of the tensor-core entry points.

@@ -3,15 +3,14 @@ device-driven transport (csrc/ep.cu).
 
 `ep.ExpertParallel` mirrors the reference: one process drives all GPUs with a thread per rank,
 events between streams and one host read per layer. `DistributedExpertParallel` is the form for
-one process per GPU: every rank maps every other rank's window (CUDA IPC), a layer is nine
-launches on the rank's stream, and the host never reads anything back:
+one process per GPU: every rank maps every other rank's window (CUDA IPC), a layer is six
+launches on the rank's stream (five up to 16 tokens), and the host never reads anything back:
 
     router GEMM, route, sort                      (local tokens, global expert ids)
-    ep_dispatch                                   rows -> owners' mailboxes, arrival flags
-    ep_wait_build                                 wait for all senders, build row groups
+    ep_dispatch_build                             rows -> owners' mailboxes, arrival flags; the last block
+                                                  waits for all senders and builds the row groups
     expert_ffn                                    both projections; results stored straight into the senders' y
-    ep_signal                                     return flags
-    ep_wait, combine                              wait for all owners, sum in expert order
+    ep_combine                                    return flags, wait for all owners, sum in expert order
 
 The arithmetic per row and the order of the combine are those of the single-GPU layer with the
 same `mode`, so every rank's output is bit-identical to `kernels.moe_layer` on its own tokens.
@@ -20,6 +19,7 @@ torch.distributed is used at set-up only (to exchange the 64-byte IPC handles) a
 data path."""
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -92,13 +92,15 @@ class DistributedExpertParallel:
     (collective). max_tokens bounds the tokens any single rank passes to layer()."""
 
     def __init__(self, num_experts, top_k, norm_topk_prob, hidden, inter, max_tokens, dtype=torch.float16,
-                 mode="gemv", device=None, group=None, logit_bias=None, backend=None):
+                 mode="gemv", device=None, group=None, logit_bias=None, backend=None, fused_transport=True):
         self.group = group
         self.rank, self.R = dist.get_rank(group), dist.get_world_size(group)
         assert num_experts % self.R == 0, "experts must split evenly over the ranks"
         assert mode in ("gemv", "gemm", "auto"), "mode: gemv, gemm, or auto (by this rank's token count)"
         self.E, self.per, self.k, self.norm = num_experts, num_experts // self.R, top_k, norm_topk_prob
         self.H, self.I, self.dtype, self.mode = hidden, inter, dtype, mode
+        # False: the five transport steps as separate launches (dispatch, wait+build, signal, wait, combine)
+        self.fused_transport = fused_transport and os.environ.get("SY_EP_SEPARATE_LAUNCHES") != "1"
         self.backend = backend if backend is not None else CudaBackend(device)
         self.device = self.backend.device
         self.max_tokens = max_tokens
@@ -174,19 +176,42 @@ class DistributedExpertParallel:
             mode = "gemv" if N * self.R * self.k * 4 <= 64 * self.E else "gemm"
         shape = 1 if mode == "gemm" else 0
         with self.backend.stream() as stream:
-            _lib.check(lib.sy_ep_dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M, per,
-                                          R, H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst, self.arrive_dst,
-                                          self.p_done, epoch, stream), "ep_dispatch")
             G = R * per
             begins, ends = self.groups.data_ptr(), self.groups.data_ptr() + 4 * G
-            _lib.check(lib.sy_ep_wait_build(self.p_arrive, self.p_meta, per, R, cap, self.y_dst, H * self.elem, epoch,
-                                            begins, ends, self.c_table.data_ptr(), stream), "ep_wait_build")
+            if not self.fused_transport:
+                return self._layer_separate_launches(h, token, wsorted, offsets, pos_of, idx, N, M, gate_up, down, code,
+                                                     shape, stream)
+            # dispatch; its last block waits for every sender's rows and builds the row groups
+            _lib.check(lib.sy_ep_dispatch_build(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M,
+                                                per, R, H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst,
+                                                self.arrive_dst, self.p_done, epoch, self.p_arrive, self.p_meta,
+                                                self.y_dst, H * self.elem, begins, ends, self.c_table.data_ptr(), stream),
+                       "ep_dispatch_build")
             _lib.check(lib.sy_expert_ffn(self.p_x, None, gate_up.data_ptr(), down.data_ptr(), begins, ends, G, R, R * cap,
                                          H, self.I, self.p_w, self.act.data_ptr(), None, self.c_table.data_ptr(),
                                          self.ffn_scratch.data_ptr(), code, shape, stream), "expert_ffn")
-            _lib.check(lib.sy_ep_signal(self.ret_dst, R, epoch, stream), "ep_signal")
-            _lib.check(lib.sy_ep_wait(self.p_ret, R, epoch, stream), "ep_wait")
-        return ext.combine(self.y, pos_of, idx, N)
+            # tell the senders their results are in place, wait for this rank's own, sum in expert order
+            out = self.backend.empty((N, H), self.dtype)
+            _lib.check(lib.sy_ep_combine(self.ret_dst, self.p_ret, R, epoch, self.y.data_ptr(), pos_of.data_ptr(),
+                                         idx.data_ptr(), N, self.k, H, out.data_ptr(), code, stream), "ep_combine")
+        return out
+
+    def _layer_separate_launches(self, h, token, wsorted, offsets, pos_of, idx, N, M, gate_up, down, code, shape, stream):
+        """The same layer with every transport step as its own launch."""
+        lib, R, per, cap, H, epoch = self.lib, self.R, self.per, self.cap, self.H, self.p_epoch
+        G = R * per
+        begins, ends = self.groups.data_ptr(), self.groups.data_ptr() + 4 * G
+        _lib.check(lib.sy_ep_dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), M, per, R,
+                                      H * self.elem, cap, self.x_dst, self.w_dst, self.meta_dst, self.arrive_dst,
+                                      self.p_done, epoch, stream), "ep_dispatch")
+        _lib.check(lib.sy_ep_wait_build(self.p_arrive, self.p_meta, per, R, cap, self.y_dst, H * self.elem, epoch, begins,
+                                        ends, self.c_table.data_ptr(), stream), "ep_wait_build")
+        _lib.check(lib.sy_expert_ffn(self.p_x, None, gate_up.data_ptr(), down.data_ptr(), begins, ends, G, R, R * cap, H,
+                                     self.I, self.p_w, self.act.data_ptr(), None, self.c_table.data_ptr(),
+                                     self.ffn_scratch.data_ptr(), code, shape, stream), "expert_ffn")
+        _lib.check(lib.sy_ep_signal(self.ret_dst, R, epoch, stream), "ep_signal")
+        _lib.check(lib.sy_ep_wait(self.p_ret, R, epoch, stream), "ep_wait")
+        return self.ext.combine(self.y, pos_of, idx, N)
 
     def close(self):
         self.backend.sync()

@@ -19,7 +19,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, sizes_per_layer, out):
+def _rank_main(rank, world, port, sizes_per_layer, fused, out):
     import torch.distributed as dist
     from oracle import ep_dist_mock as mock
     from switchyard_b200.ep_dist import DistributedExpertParallel
@@ -34,7 +34,7 @@ def _rank_main(rank, world, port, sizes_per_layer, out):
         dn = (torch.randn(E, H, I, generator=g) * 0.3).half()
         per = E // world
         ep = DistributedExpertParallel(E, k, False, H, I, max_tokens=max(max(s) for s in sizes_per_layer),
-                                       dtype=torch.float16, mode="gemv", backend=backend)
+                                       dtype=torch.float16, mode="gemv", backend=backend, fused_transport=fused)
         ok = True
         for layer_no, sizes in enumerate(sizes_per_layer):
             h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).half()
@@ -50,13 +50,15 @@ def _rank_main(rank, world, port, sizes_per_layer, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,sizes", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)]), (4, [(3, 7, 0, 2), (8, 8, 8, 8)])])
-def test_protocol_over_gloo_processes(world, sizes):
+@pytest.mark.parametrize("world,sizes,fused", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], True),
+                                               (2, [(5, 9), (0, 3), (1, 0)], False),
+                                               (4, [(3, 7, 0, 2), (8, 8, 8, 8)], True)])
+def test_protocol_over_gloo_processes(world, sizes, fused):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, out)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, fused, out)) for r in range(world)]
     for p in procs:
         p.start()
     results = [out.get(timeout=180) for _ in procs]

@@ -24,15 +24,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, sizes_per_layer, mode, dtype_name, out):
+def _worker(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out):
     try:
-        _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, out)
+        _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out)
     except BaseException:  # report instead of leaving the parent waiting for a result
         import traceback
         out.put((rank, False, traceback.format_exc()))
 
 
-def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, out):
+def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out):
     import torch.distributed as dist
     from switchyard_b200 import kernels
     from switchyard_b200.ep_dist import DistributedExpertParallel
@@ -48,7 +48,7 @@ def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, out):
         per = E // world
         my_gu, my_dn = gu[rank * per:(rank + 1) * per].contiguous(), dn[rank * per:(rank + 1) * per].contiguous()
         ep = DistributedExpertParallel(E, k, False, H, I, max_tokens=max(max(s) for s in sizes_per_layer), dtype=dtype,
-                                       mode=mode)
+                                       mode=mode, fused_transport=fused)
         ok = True
         for layer_no, sizes in enumerate(sizes_per_layer):
             hs = [torch.randn(n, H, generator=cases.gen(100 * layer_no + r)).to(dtype) for r, n in enumerate(sizes)]
@@ -64,12 +64,12 @@ def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, out):
         dist.destroy_process_group()
 
 
-def run(world, sizes_per_layer, mode, dtype_name="float16"):
+def run(world, sizes_per_layer, mode, dtype_name="float16", fused=True):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, sizes_per_layer, mode, dtype_name, out))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, sizes_per_layer, mode, dtype_name, fused, out))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -92,6 +92,11 @@ def test_two_ranks_bit_identical(mode):
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
 def test_two_ranks_bf16():
     run(2, [(33, 12), (12, 33)], "gemv", "bfloat16")
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
+def test_two_ranks_with_every_transport_step_as_its_own_launch():
+    run(2, [(7, 30), (0, 5), (64, 3)], "gemv", fused=False)
 
 
 @pytest.mark.skipif(n_gpus() < 4, reason="needs four GPUs")
