@@ -319,7 +319,9 @@ def run_single_gpu(args):
         "e2e": {"value": e2e_bytes / (e2e_ms / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                 "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms / args.steps,
                 "api": "switchyard_b200.kernels.moe_layer, eager, host buffers pinned"},
-        "gpu_launches": args.steps * len(SWEEP) * 4,
+        # this library's kernels in the timed region, per layer pass: route + sort (one launch up to
+        # 16 tokens), fused expert FFN, combine; the cuBLAS router GEMM is not counted
+        "gpu_launches": args.steps * sum(3 if T <= kernels.ROUTE_SORT_MAX_TOKENS else 4 for T in SWEEP),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_TRAFFIC_BYTES, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, streaming shape>, fused FFN (sy_expert_ffn)",
                      "workload": "T=64, gate/up + down projections of one layer in one launch, weight sets in rotation",

@@ -182,7 +182,9 @@ def run(args):
             "e2e": {"value": e2e_bytes / (float(e2e_t) / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                     "d2h_bytes_per_step": io_bytes, "ms_per_step": float(e2e_t) / args.steps,
                     "api": "switchyard_b200.ep_dist.DistributedExpertParallel.layer, host buffers pinned"},
-            "gpu_launches": args.steps * len(SWEEP) * 9 * world,
+            # this library's kernels per layer and rank: route (+ sort: one launch up to 16 tokens),
+            # dispatch+build, expert FFN, signal+wait+combine; the cuBLAS router GEMM is not counted
+            "gpu_launches": args.steps * sum(4 if T <= kernels.ROUTE_SORT_MAX_TOKENS else 5 for T in SWEEP) * world,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_source": peak_src,
                          "kernel": "whole expert-parallel layer, per GPU (the weight-stream kernel is profiled at N=1)"},
