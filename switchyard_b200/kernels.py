@@ -335,3 +335,43 @@ def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
         return X.combine(y, pos_of, idx, N)
     idx, w = route(h, router, top_k, norm_topk_prob)
     return experts(h, idx, w, gate_up, down, mode)
+
+
+class GraphedLayer:
+    """moe_layer for one layer's weights with the launches of every batch size captured once in a
+    CUDA graph and replayed afterwards: what a decode loop does with its layers (the reference
+    captures its decode step the same way). Call it with h [N,H], on the device or in pinned
+    host memory; the result is a buffer owned by this object (valid until the next call with
+    the same N), or is copied into `out` (device or pinned host memory) when given. Everything is
+    enqueued on the current stream; nothing synchronises."""
+
+    def __init__(self, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
+        self.args = (router, gate_up, down, top_k, norm_topk_prob, mode)
+        self.device = gate_up.device
+        self.graphs = {}  # N -> (graph, static input, static output)
+
+    def _capture(self, N, dtype):
+        router, gate_up, down, top_k, norm, mode = self.args
+        x = torch.zeros(N, gate_up.shape[2], dtype=dtype, device=self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # first use loads the library, cuBLAS picks its kernel
+                moe_layer(x, router, gate_up, down, top_k, norm, mode)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                y = moe_layer(x, router, gate_up, down, top_k, norm, mode)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self.graphs[N] = (g, x, y)
+        return self.graphs[N]
+
+    def __call__(self, h, out=None):
+        N = h.shape[0]
+        g, x, y = self.graphs.get(N) or self._capture(N, h.dtype)
+        x.copy_(h, non_blocking=True)
+        g.replay()
+        if out is None:
+            return y
+        out.copy_(y, non_blocking=True)
+        return out

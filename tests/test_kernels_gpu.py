@@ -303,6 +303,58 @@ def test_olmoe_decode_layer(K, olmoe, tokens, mode):
 
 
 # ------------------------------------------------------------------------------ transport
+@pytest.mark.parametrize("tokens,dtype", [(4096, torch.bfloat16), (2048, torch.float16)])
+def test_olmoe_prefill_layer_at_full_size(K, olmoe, tokens, dtype):
+    """The prefill configuration at its real size (hidden 2048, 64 experts of width 1024, top-8,
+    Zipf-skewed routing: the busiest expert gets about four times the mean), checked on a sample
+    of tokens against the float32 expert loop; both compute tiles must give the same bits."""
+    import os
+    from switchyard_b200 import synthetic
+    router, gu, dn = (t.to(dtype) for t in olmoe)
+    h = synthetic.hidden_states(tokens, "cpu", dtype, seed=tokens)
+    rd, gud, dnd, hd = router.to(DEV), gu.to(DEV), dn.to(DEV), h.to(DEV)
+    logits = (torch.nn.functional.linear(hd, rd) + synthetic.zipf_bias().to(DEV).to(dtype)).contiguous()
+    idx, w = K.ext().route(logits, 8, False)
+    outs = []
+    for tile in ("single", "pair"):
+        os.environ["SY_GEMM_TILE"] = tile
+        try:
+            outs.append(K.experts(hd, idx, w, gud, dnd, "gemm"))
+        finally:
+            os.environ.pop("SY_GEMM_TILE", None)
+    assert torch.equal(outs[0], outs[1])
+    assert K.ext().device_status() == 0
+    counts = torch.bincount(idx.flatten().long().cpu(), minlength=64)
+    assert counts.max().item() > 3 * counts.float().mean().item()  # the skew is there
+    sample = torch.arange(0, tokens, tokens // 16)
+    hs, ids, ws = h[sample], idx.cpu()[sample].long(), w.cpu()[sample]
+    want = mo.experts_reference(hs.float(), ids, ws.float(), gu.float(), dn.float())
+    loop16 = mo.experts_reference(hs, ids, ws, gu, dn)
+    got = outs[0].cpu()[sample].float()
+    err = (got - want).abs().max().item()
+    err16 = (loop16.float() - want).abs().max().item()
+    floor = 2e-3 if dtype == torch.float16 else 1.6e-2
+    assert err <= max(2 * err16, floor), (err, err16)
+
+
+def test_graphed_layer_replays_the_same_bits(K):
+    """GraphedLayer captures moe_layer once per batch size; replays, from device or pinned host
+    input, give moe_layer's bits for new inputs of that size."""
+    _, router, gu, dn = cases.layer_inputs(8)
+    rd, gud, dnd = router.to(DEV), gu.to(DEV), dn.to(DEV)
+    layer = K.GraphedLayer(rd, gud, dnd, 8, False, "auto")
+    for N in (5, 40, 5, 40, 200):
+        for seed in (1, 2):
+            h = torch.randn(N, rd.shape[1], generator=cases.gen(1000 * seed + N)).half()
+            want = K.moe_layer(h.to(DEV), rd, gud, dnd, 8, False, "auto")
+            assert torch.equal(layer(h.to(DEV)), want)
+            out = torch.empty(N, rd.shape[1], dtype=torch.float16).pin_memory()
+            layer(h.pin_memory(), out=out)
+            torch.cuda.synchronize()
+            assert torch.equal(out, want.cpu())
+    assert len(layer.graphs) == 3
+
+
 def test_gather_rows_and_copy(K):
     src = torch.randn(100, 256, generator=cases.gen(1)).half().to(DEV)
     index = torch.randint(0, 100, (37,), generator=cases.gen(2)).int().to(DEV)
