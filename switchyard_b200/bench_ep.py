@@ -208,7 +208,7 @@ def run_config(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     if args.config == "ep256":
-        dtype, sizes, mode = torch.float16, (256,), "gemm" if world == 1 else "gemv"
+        dtype, sizes, mode = torch.float16, (256,), kernels.auto_mode(256 * TOPK, E)
     else:
         dtype, sizes, mode = torch.bfloat16, (1024, 4096, 8192), "gemm"
     per = E // world
@@ -220,8 +220,7 @@ def run_config(args):
         h = synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T)
         if world > 1:
             from .ep_dist import DistributedExpertParallel
-            # with 64/R rows per expert per token-batch the streaming shape holds up to 64 rows a tile
-            m = "gemv" if T * world * TOPK * 4 // E <= 64 else "gemm"
+            m = kernels.auto_mode(T * world * TOPK, E)
             ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode=m, device=dev,
                                            logit_bias=bias)
             run = lambda l: ep.layer(h, *layers[l])
@@ -239,14 +238,26 @@ def run_config(args):
             for i in range(max(args.warmup, 3)):
                 run(i % n_sets)
             torch.cuda.synchronize()
+            # one CUDA graph per weight set: the host's launch cost (some 100 us for the layer's
+            # dozen launches and allocations) would otherwise bound the smaller batches
+            graphs, keep = [], []
+            for l in range(n_sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    keep.append(run(l))
+                graphs.append(g)
+            for i in range(max(args.warmup, 3)):
+                graphs[i % n_sets].replay()
+            torch.cuda.synchronize()
             if world > 1:
                 dist.barrier()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record(stream)
             for i in range(args.steps):
-                run(i % n_sets)
+                graphs[i % n_sets].replay()
             t1.record(stream)
             torch.cuda.synchronize()
+            del graphs, keep
         ms = torch.tensor([t0.elapsed_time(t1) / args.steps], dtype=torch.float64, device=dev)
         # routing skew actually achieved (rank 0's tokens)
         idx, _ = kernels.ext().route((torch.nn.functional.linear(h, layers[0][0]) + bias.to(dev).to(dtype)).contiguous(),
@@ -262,7 +273,7 @@ def run_config(args):
                     "mode": mode_used, "busiest_over_mean": skew})
     if rank == 0:
         print(json.dumps({"config": args.config, "n_gpus": world, "dtype": str(dtype).replace("torch.", ""),
-                          "steps": args.steps, "timing": "CUDA events, eager launches, max over ranks",
+                          "steps": args.steps, "timing": "CUDA events around CUDA-graph replays of the whole layer, max over ranks",
                           "results": out, "device_status": kernels.ext().device_status(dev)}), flush=True)
     if world > 1:
         dist.destroy_process_group()

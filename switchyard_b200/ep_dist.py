@@ -172,8 +172,8 @@ class DistributedExpertParallel:
         M = N * self.k
         code = _lib.SY_DTYPE_F16 if self.dtype == torch.float16 else _lib.SY_DTYPE_BF16
         mode = self.mode
-        if mode == "auto":  # rows per expert ~ tokens * ranks * k / E; keep 4x headroom for skew within a 64-row tile
-            mode = "gemv" if N * self.R * self.k * 4 <= 64 * self.E else "gemm"
+        if mode == "auto":  # every rank brings about as many rows as this one: rows per expert ~ tokens * ranks * k / E
+            mode = kernels.auto_mode(N * self.R * self.k, self.E)
         shape = 1 if mode == "gemm" else 0
         with self.backend.stream() as stream:
             G = R * per
