@@ -182,6 +182,20 @@ def test_layer_matches_the_fp32_expert_loop(K, N, skew, mode, dtype):
     assert err <= max(2 * err16, floor), (err, err16, rel)
 
 
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+@pytest.mark.parametrize("N", [5, 150, 700])
+def test_sizes_that_fill_no_tile(K, mode, N):
+    """hidden 200 (three 64-wide k blocks and a tail of 8), expert width 72 (less than any tile's
+    columns), 16 experts, top-4: every tile is ragged in k, in columns and in rows."""
+    h, router, gu, dn = cases.layer_inputs(N, E=16, k=4, H=200, I=72, seed=3, skew=1.0)
+    ridx, rw = mo.route_reference(h, router, 4, False)
+    want = mo.experts_reference(h.float(), ridx, rw.float(), gu.float(), dn.float())
+    loop16 = mo.experts_reference(h, ridx, rw, gu, dn)
+    err, err16, rel = layer_errors(K, h, router, gu, dn, mode, ridx, rw, want, loop16)
+    assert err <= max(2 * err16, 2e-3), (err, err16, rel)
+    assert K.ext().device_status() == 0
+
+
 def test_empty_experts_and_a_single_token(K):
     h, router, gu, dn = cases.layer_inputs(1)
     out = K.moe_layer(h.to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False)
