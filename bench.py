@@ -342,6 +342,8 @@ def run_case(spec):
     mode, T = parts[0], int(parts[1])
     dtype = torch.bfloat16 if "bf16" in parts[2:] else torch.float16
     dev = torch.device("cuda:0")
+    if mode == "ep":
+        return run_case_ep(spec, T, dtype, dev)
     layers = [synthetic.layer_weights(dev, dtype, seed=100 + l) for l in range(2)]
     h = synthetic.hidden_states(T, dev, dtype, seed=T)
     bias = synthetic.zipf_bias().to(dev).to(dtype) if "zipf" in parts[2:] else None
@@ -358,13 +360,35 @@ def run_case(spec):
                       "device_status": kernels.ext().device_status(dev)}))
 
 
+def run_case_ep(spec, T, dtype, dev):
+    """--case ep:T: the one-process-per-GPU expert-parallel layer with a single rank (all 64
+    experts local, every row "sent" to this GPU's own mailbox), three passes: the transport
+    kernels (dispatch + build, signal + wait + combine) run on one GPU without a peer to wait for."""
+    import torch.distributed as dist
+    from switchyard_b200 import kernels, synthetic
+    from switchyard_b200.ep_dist import DistributedExpertParallel
+    torch.cuda.set_device(dev)
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29599", rank=0, world_size=1)
+    layers = [synthetic.layer_weights(dev, dtype, seed=100 + l) for l in range(2)]
+    h = synthetic.hidden_states(T, dev, dtype, seed=T)
+    ep = DistributedExpertParallel(64, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode="auto", device=dev)
+    for i in range(3):
+        out = ep.layer(h, *layers[i % 2])
+    torch.cuda.synchronize()
+    same = bool(torch.equal(out, kernels.moe_layer(h, *layers[0], TOPK, False, "auto")))
+    print(json.dumps({"case": spec, "checksum": float(out.float().abs().sum()), "equals_single_gpu_layer": same,
+                      "device_status": kernels.ext().device_status(dev)}))
+    ep.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] - run one small layer shape (for profiling)")
+    ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] (MODE gemv | gemm | ep) - run one small layer shape (for profiling)")
     ap.add_argument("--config", default="decode", choices=["decode", "ep256", "prefill", "model"],
                     help="decode = the bench line (configs[1]); ep256 / prefill = configs[2] / configs[3], reported in DESIGN.md")
     args = ap.parse_args()
