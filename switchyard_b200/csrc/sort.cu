@@ -24,7 +24,7 @@ constexpr int SORT_THREADS = 512;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int SORT_MAX_E = 256;
 constexpr int SORT_SINGLE_MAX = 8192;       // choices one block sorts by itself
-constexpr int SORT_CHUNK = 4096;            // target choices per block when several blocks sort
+constexpr int SORT_CHUNK = 1024;            // target choices per block when several blocks sort
 constexpr int SORT_MAX_BLOCKS = 128;        // scratch table rows that launch 2 keeps in shared memory
 
 struct SortShape {
