@@ -390,7 +390,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] (MODE gemv | gemm | ep) - run one small layer shape (for profiling)")
     ap.add_argument("--config", default="decode", choices=["decode", "ep256", "prefill", "model"],
-                    help="decode = the bench line (configs[1]); ep256 / prefill = configs[2] / configs[3], reported in DESIGN.md")
+                    help="decode = the bench line (configs[1]); ep256 / prefill / model = configs[2] / configs[3] / configs[4]")
     args = ap.parse_args()
     if args.case:
         return run_case(args.case)

@@ -194,7 +194,7 @@ def run(args):
 
 
 # ------------------------------------------------------------------------------------------
-# The other benchmark configurations (reported in DESIGN.md; the driver's bench line is the
+# The other benchmark configurations (the default bench line is the
 # decode sweep above): config 3 = 256 tokens per GPU, fp16, Zipf-skewed routing;
 # config 4 = prefill, 1024 / 4096 / 8192 tokens per GPU, bf16, same skew.
 def run_config(args):
