@@ -17,8 +17,15 @@ in rotation), so a pass never finds its weights in L2.
   roofline the dominant kernel (the fused expert FFN of T=64: both weight streams in one launch)
           alone: algorithmic bytes per launch / its CUDA-event duration, against the measured
           HBM copy bandwidth;
-  cpu_baseline / --impl reference: the float32 expert loop of the CPU oracle on the same
-          sweep, on the host cores.
+  prefill the same layer in bf16 at 4096 and 8192 tokens with Zipf-skewed routing (compute-bound:
+          the tensor-core shape of the expert kernel), TFLOP/s against the measured cuBLAS rate;
+  cpu_baseline / --impl reference: the reference's float32 expert loop (`switchyard.moe`,
+          imported unchanged from `baseline/_ref` when `python tests/fetch_reference.py` has put
+          a copy there; otherwise its restatement in oracle/moe_oracle.py) on the same sweep, on
+          the host cores.
+
+`--case MODE:T[...]` runs three passes of one layer shape and nothing else: the small,
+self-ending workload that the ncu summaries under profiles/ are captured from.
 
 Prints ONE JSON line on rank 0."""
 
@@ -38,11 +45,26 @@ sys.path.insert(0, ROOT)
 SWEEP = (1, 8, 32, 64)
 H, I, E, TOPK = 2048, 1024, 64, 8
 EXPERT_BYTES = 3 * H * I * 2          # fp16 bytes of one expert's weights
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused expert-FFN launch at T=64 (all 64 experts
-# used) from the ncu capture summarised in profiles/expert_ffn_decode_T64_fp16.md
-NCU_TRAFFIC_BYTES = 805.65e6 + 4.94e6
 LAYERS = 8                             # resident weight sets used in rotation (8 x 805 MB)
 METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
+# The workload, in the words both arms print (the GPU arm and `--impl reference`).
+CONFIG = {"workload": "configs[1]: OLMoE MoE layer decode sweep T=1,8,32,64 (fp16 on the GPU, the reference's "
+                      "float32 expert loop on the host); a step = one layer pass at each T",
+          "tokens": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK,
+          "l2": f"GPU arm: inputs larger than L2, passes rotate over {LAYERS} resident weight sets of 805 MB; "
+                "host arm: one float32 weight set",
+          "seeds": {"weights": "100 + weight set", "hidden": "T"}}
+
+
+def ncu_traffic():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture (a number
+    measured once under ncu; the file names the capture it came from), or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "expert_ffn_decode_T64_fp16.json")) as f:
+            rec = json.load(f)
+        return float(rec["dram_bytes_per_launch"]), rec.get("source")
+    except Exception:
+        return None, None
 
 
 def peaks():
@@ -52,6 +74,17 @@ def peaks():
         return float(p["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def tensor_peak():
+    """Sustained dense bf16 rate of cuBLAS on this pool's B200 (TFLOP/s): the prefill layer runs
+    for hundreds of microseconds back to back, so the sustained figure is its denominator."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -105,57 +138,78 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_sweep_inputs(seed=0):
-    """float32 weights and hidden states of the sweep on the host (same distributions)."""
-    g = torch.Generator().manual_seed(seed)
+def reference_math():
+    """(route, experts, kind): the reference's own `switchyard.moe` when a copy of the reference
+    sits in baseline/_ref (kind "reference"), else its restatement in oracle/ (kind "port")."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.exists(os.path.join(ref, "switchyard", "moe.py")):
+        try:
+            sys.path.insert(0, ref)
+            from switchyard import moe
+            return moe.route, moe.experts_reference, "reference"
+        except Exception:
+            pass
+        finally:
+            sys.path.remove(ref)
+    from oracle import moe_oracle as mo
+    return mo.route_reference, mo.experts_reference, "port"
+
+
+def cpu_sweep_inputs():
+    """float32 weights and hidden states of the sweep on the host: weight set 0 and the hidden
+    states of the GPU arm (same seeds, same distributions; generated on the CPU)."""
+    g = torch.Generator().manual_seed(100)
     router = torch.randn(E, H, generator=g) * 0.02
-    gate_up = torch.randn(E, 2 * I, H, generator=g) * 0.02
-    down = torch.randn(E, H, I, generator=g) * 0.02
-    hs = {T: torch.randn(T, H, generator=g) for T in SWEEP}
+    gate_up = torch.empty(E, 2 * I, H)
+    down = torch.empty(E, H, I)
+    for e in range(E):
+        gate_up[e] = torch.randn(2 * I, H, generator=g) * 0.02
+        down[e] = torch.randn(H, I, generator=g) * 0.02
+    hs = {T: torch.randn(T, H, generator=torch.Generator().manual_seed(T)) for T in SWEEP}
     return router, gate_up, down, hs
 
 
-def cpu_sweep_once(mo, router, gate_up, down, hs):
+def cpu_sweep_once(route, experts, router, gate_up, down, hs):
     """One sweep of the float32 reference loop; returns (seconds, algorithmic fp16 bytes)."""
     total_bytes, t0 = 0, time.perf_counter()
     for T in SWEEP:
-        idx, w = mo.route_reference(hs[T], router, TOPK, False)
-        mo.experts_reference(hs[T], idx, w, gate_up, down)
+        idx, w = route(hs[T], router, TOPK, False)
+        experts(hs[T], idx, w, gate_up, down)
         total_bytes += int(torch.unique(idx).numel()) * EXPERT_BYTES
     return time.perf_counter() - t0, total_bytes
 
 
 def cpu_leg(sweeps, warmup=1):
-    from oracle import moe_oracle as mo
+    route, experts, kind = reference_math()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     router, gate_up, down, hs = cpu_sweep_inputs()
     for _ in range(warmup):
-        cpu_sweep_once(mo, router, gate_up, down, hs)
+        cpu_sweep_once(route, experts, router, gate_up, down, hs)
     times, nbytes = [], 0
     for _ in range(sweeps):
-        dt, nbytes = cpu_sweep_once(mo, router, gate_up, down, hs)
+        dt, nbytes = cpu_sweep_once(route, experts, router, gate_up, down, hs)
         times.append(dt)
-    return times, nbytes, torch.get_num_threads()
+    return times, nbytes, torch.get_num_threads(), kind
 
 
 def run_reference(args):
     """--impl reference: the reference's CPU implementation of the path (its float32 expert
-    loop, restated in oracle/moe_oracle.py) on the host cores, one sweep per step."""
+    loop) on the host cores, one sweep per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    times, nbytes, threads = cpu_leg(args.steps, args.warmup)
+    times, nbytes, threads, kind = cpu_leg(args.steps, args.warmup)
     total = sum(times)
     value = nbytes * len(times) / total / 1e9
+    source = "switchyard.moe of the reference, imported unchanged" if kind == "reference" else "oracle/moe_oracle.py"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(times) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1] decode sweep T=1,8,32,64 on the host: float32 reference expert loop",
-                   "tokens": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{len(times)} sweeps of T=1,8,32,64, float32, torch CPU"},
+        "config": CONFIG,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"{len(times)} sweeps of T=1,8,32,64, float32 expert loop ({source}), torch CPU"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -271,25 +325,24 @@ def run_single_gpu(args):
     e2e_ms = e0.elapsed_time(e1)
     io_bytes = sum(T * H * 2 for T in SWEEP)
 
-    # ---- the dominant kernel alone: the fused expert FFN (both weight streams) of T=64, one
-    # launch per weight set in rotation, CUDA events around each launch on the launch stream
+    # ---- the dominant kernel alone: the fused expert launch of T=64 (both weight streams and the
+    # combine in its epilogue: the launch the layer runs), one launch per weight set in rotation
     T = SWEEP[-1]
     ext = kernels.ext()
     kern_ms, kern_bytes = [], []
     with torch.cuda.stream(stream):
         sorted_in = []
         for l, (router, gu, dn) in enumerate(layers):
-            idx, w = kernels.route(hs[T], router, TOPK, False)
-            counts, offsets, token, wsorted, pos_of = ext.sort_by_expert(idx, w, E)
-            sorted_in.append((token, offsets, wsorted))
+            idx, w, counts, offsets, token, wsorted, pos_of = kernels.route_and_sort(hs[T], router, TOPK, False)
+            sorted_in.append((token, offsets, wsorted, pos_of))
         # One pair of events around a full rotation of back-to-back launches: with a single launch
         # between the events the host's launch latency (about 10 us) would be counted as kernel time.
         for rep in range(max(args.steps // 2, 4) + 2):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             for l in range(LAYERS):
-                token, offsets, wsorted = sorted_in[l]
-                ext.expert_ffn(hs[T], token, layers[l][1], layers[l][2], offsets, T * TOPK, wsorted, 0)
+                token, offsets, wsorted, pos_of = sorted_in[l]
+                ext.expert_ffn_combine(hs[T], token, layers[l][1], layers[l][2], offsets, wsorted, pos_of, TOPK)
             b.record(stream)
             stream.synchronize()
             if rep >= 2:
@@ -299,39 +352,88 @@ def run_single_gpu(args):
     achieved = sum(kern_bytes) / (sum(kern_ms) / 1e3) / 1e9
     assert ext.device_status(dev) == 0
 
+    # ---- prefill: the same layer, compute-bound (bf16, Zipf-skewed routing), graph replays
+    del graphs, graphed, outs, layers
+    torch.cuda.empty_cache()
+    prefill = prefill_leg(dev, stream, steps=max(args.steps // 2, 6))
+
     # ---- CPU baseline (bounded sample of the same sweep)
-    cpu_times, cpu_bytes, threads = cpu_leg(sweeps=20, warmup=1)
+    cpu_times, cpu_bytes, threads, cpu_kind = cpu_leg(sweeps=20, warmup=1)
     cpu_value = cpu_bytes * len(cpu_times) / sum(cpu_times) / 1e9
+    traffic, traffic_src = ncu_traffic()
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "configs[1]: OLMoE MoE layer decode sweep T=1,8,32,64, fp16, grouped_gemv path; "
-                               "a step = one layer pass at each T",
-                   "tokens": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK, "mode": mode,
-                   "l2": f"inputs larger than L2: passes rotate over {LAYERS} resident weight sets of 805 MB",
-                   "timing": "CUDA events on the launch stream around CUDA-graph replays of the whole layer",
-                   "seeds": {"weights": "100+layer", "hidden": "T"}},
+        "config": CONFIG,
+        "arm": {"mode": mode, "path": "route_fused (router GEMM + route + sort) -> expert_ffn_combine (tcgen05 weight "
+                                      "stream, combine in the epilogue): two launches per layer",
+                "timing": "CUDA events on the launch stream around CUDA-graph replays of the whole layer"},
         "sweep": sweep,
         "vs_nominal_8TBps": value / 8000.0,
         "clocks": clocks,
         "e2e": {"value": e2e_bytes / (e2e_ms / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                 "d2h_bytes_per_step": io_bytes, "ms_per_step": e2e_ms / args.steps,
                 "api": "switchyard_b200.kernels.GraphedLayer (moe_layer captured per batch size), host buffers pinned, H2D and D2H every step"},
-        # this library's kernels in the timed region, per layer pass: route + sort (one launch up to
-        # 16 tokens), fused expert FFN, combine; the cuBLAS router GEMM is not counted
-        "gpu_launches": args.steps * sum(3 if T <= kernels.ROUTE_SORT_MAX_TOKENS else 4 for T in SWEEP),
+        # this library's kernels in the timed region, per layer pass: route_fused, expert_ffn_combine
+        "gpu_launches": args.steps * 2 * len(SWEEP),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES, "peak_source": peak_src, "kernel": "gemm_umma_kernel<half, streaming shape>, fused FFN (sy_expert_ffn)",
-                     "workload": "T=64, gate/up + down projections of one layer in one launch, weight sets in rotation",
+                     "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src,
+                     "kernel": "gemm_umma_kernel<half, streaming shape>: gate/up + down projections + combine (sy_expert_ffn_combine)",
+                     "workload": "T=64, one layer's experts in one launch, weight sets in rotation",
                      "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
                      "vs_nominal_8TBps": achieved / 8000.0},
-        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{len(cpu_times)} sweeps of T=1,8,32,64, float32 expert loop (oracle), torch CPU",
+        "prefill": prefill,
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": threads, "kind": cpu_kind,
+                         "sample": f"{len(cpu_times)} sweeps of T=1,8,32,64, float32 expert loop, torch CPU",
                          "ms_per_sweep": statistics.median(cpu_times) * 1e3},
     }
     print(json.dumps(line), flush=True)
+
+
+def prefill_leg(dev, stream, steps):
+    """configs[3] at one GPU: the layer in bf16 at 4096 and 8192 tokens, Zipf-skewed routing
+    (busiest expert about four times the mean), whole layer (router GEMM to combine) replayed from
+    CUDA graphs over three weight sets. FLOPs = rows x 12 582 912 (both projections)."""
+    from switchyard_b200 import kernels, synthetic
+    dtype, n_sets = torch.bfloat16, 3
+    layers = [synthetic.layer_weights(dev, dtype, seed=200 + l) for l in range(n_sets)]
+    bias = synthetic.zipf_bias().to(dev).to(dtype)
+    peak, peak_src = tensor_peak()
+    out = []
+    with torch.cuda.stream(stream):
+        for T in (4096, 8192):
+            h = synthetic.hidden_states(T, dev, dtype, seed=T)
+
+            def run(l):
+                srt = kernels.route_and_sort(h, layers[l][0], TOPK, False, bias)
+                return kernels._sorted_experts(h, srt, layers[l][1], layers[l][2], TOPK, "gemm")
+
+            for l in range(n_sets):
+                run(l)
+            stream.synchronize()
+            graphs, keep = [], []
+            for l in range(n_sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    keep.append(run(l))
+                graphs.append(g)
+            for i in range(3):
+                graphs[i % n_sets].replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for i in range(steps):
+                graphs[i % n_sets].replay()
+            b.record(stream)
+            stream.synchronize()
+            ms = a.elapsed_time(b) / steps
+            tflops = T * TOPK * 12582912 / (ms / 1e3) / 1e12
+            out.append({"tokens": T, "dtype": "bf16", "routing": "zipf", "ms_per_layer": ms, "tflops": tflops,
+                        "frac_of_sustained": tflops / peak, "peak_tflops": peak, "peak_source": peak_src,
+                        "tile": "pair" if T * TOPK >= E * 768 else "single", "timing": f"{steps} graph replays"})
+            del graphs, keep
+    return out
 
 
 def run_case(spec):
@@ -375,7 +477,7 @@ def run_case_ep(spec, T, dtype, dev):
     for i in range(3):
         out = ep.layer(h, *layers[i % 2])
     torch.cuda.synchronize()
-    same = bool(torch.equal(out, kernels.moe_layer(h, *layers[0], TOPK, False, "auto")))
+    same = bool(torch.equal(out, kernels.moe_layer(h, *layers[0], TOPK, False, ep.mode)))
     print(json.dumps({"case": spec, "checksum": float(out.float().abs().sum()), "equals_single_gpu_layer": same,
                       "device_status": kernels.ext().device_status(dev)}))
     ep.close()

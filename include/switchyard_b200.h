@@ -36,10 +36,20 @@ const char* sy_last_error(void);
 /* Library version string. */
 const char* sy_version(void);
 
-/* Blocks until `stream` is idle, then returns the current device's kernel status word and
- * clears it: 0, or the DeviceStatus code of the first bounded wait that gave up. Only tests
- * and error paths need it. */
+/* Blocks until `stream` is idle, then reads the current device's kernel status word into
+ * *status_out and clears it: 0, or the code of the last bounded wait that gave up (1-4: a wait
+ * inside the expert kernel's pipeline, 5: a flag, 6: an index outside its array was skipped).
+ * Returns SY_OK when the word is 0 and SY_ERR_DEVICE otherwise: the results of the kernels that
+ * ran since the last call are then not to be trusted. The stream stays usable. Cheap enough
+ * for the end of a request or a decode step; not meant for every layer. */
 int sy_device_status(void* stream, int* status_out);
+
+/* How long a kernel waits for a flag, a barrier or another block before it gives up, records
+ * a status code and lets the stream go on. One value for the whole process, used by launches
+ * made after the call. Default 2 s, or SY_WAIT_LIMIT_MS from the environment (read once).
+ * 1 us <= limit_ns <= 60 s. No counterpart in the reference (its waits are stream events). */
+int sy_set_wait_limit_ns(uint64_t limit_ns);
+uint64_t sy_wait_limit_ns(void);
 
 /* route — replaces `route` (moe_kernels.cu:73-89, kernel l.23-71).
  * logits [n_tokens, n_experts] row-major, 16-bit. One warp per token: float32 softmax,
@@ -73,6 +83,25 @@ int sy_route_sort_max_choices(void);
 int sy_route_sort(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
                   int32_t* idx, void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
                   int32_t* pos_of, void* stream);
+
+/* route_fused — router GEMM, sy_route and sy_sort_by_expert in ONE launch for decode-sized
+ * batches: replaces `F.linear(h, router)` followed by `route` (switchyard/kernels.py:30-32,
+ * moe_kernels.cu:73-89) and `sort_by_expert` (l.142-157).
+ * h 16-bit [n_tokens, hidden]; router 16-bit [n_experts, hidden]; bias 16-bit [n_experts] or
+ * NULL (added to the rounded logits in the 16-bit type, as a tensor add would).
+ * logits = round16(h . router^T) with float32 accumulation in a fixed order that depends only on
+ * the token's own row; they are written to logits_out [n_tokens, n_experts] when it is not NULL.
+ * The routing is exactly sy_route applied to those logits and the sort exactly
+ * sy_sort_by_expert, so the outputs equal the separate calls fed with logits_out. The logits
+ * themselves may differ from a library GEMM's in the last bit (another summation order).
+ * ticket: one zero-initialised int32 of device memory, left at zero; launches that share it
+ * must not overlap. Limits: n_tokens * top_k <= 8192, n_experts a multiple of 8 up to 128,
+ * hidden a multiple of 32, top_k <= 8. */
+int sy_route_fused_max_tokens(void);
+int sy_route_fused(const void* h, const void* router, const void* bias, int n_tokens, int n_experts, int hidden,
+                   int top_k, int norm_topk_prob, int dtype, void* logits_out, int32_t* idx, void* w,
+                   int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                   int32_t* ticket, void* stream);
 
 /* sort_by_expert_static — no counterpart in the reference. The same sort, same outputs bit for
  * bit, for callers that are not allowed to allocate device memory while they run and so
@@ -126,6 +155,13 @@ int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const i
                     int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
                     int dtype, void* stream);
 
+/* The compute shape has two tiles with identical results: one CTA per 128-row tile, or a CTA
+ * pair (tcgen05 cta_group::2) per 256-row tile, chosen per launch from the mean rows per expert
+ * (pairs from 768). This overrides the choice for plain sorted batches, for the whole process:
+ * 0 = automatic, 1 = one CTA, 2 = pairs. SY_GEMM_TILE=single|pair in the environment (read once,
+ * at the first launch) sets the initial value. No counterpart in the reference. */
+int sy_force_compute_tile(int tile);
+
 /* expert_ffn — the whole expert FFN of a layer in ONE launch: gate/up projection with SwiGLU
  * into `act`, then the down projection scaled by the router weights into `y`, i.e. what the
  * reference does with two grouped_gemv / grouped_gemm calls (switchyard/kernels.py:56-63). A down
@@ -141,12 +177,31 @@ int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const i
  * [rows_bound, inter] scratch; y 16-bit [rows_bound, hidden], or y_table as c_table above.
  * scratch: sy_expert_ffn_scratch_bytes(experts) bytes, zero before the first call; the kernel
  * leaves it zero again. Calls that share one scratch must not overlap (one per stream).
- * compute_shape: 0 = streaming shape (decode), 1 = compute shape (prefill). */
+ * compute_shape: 0 = streaming shape (decode), 1 = compute shape (prefill).
+ * The launch is one persistent block per SM (or pair of SMs) whose blocks wait for one another,
+ * sized by an occupancy query: all of them must be resident at once. Do not overlap it on the
+ * same GPU with another kernel that holds most of an SM's shared memory (the waits are bounded:
+ * the cost would be a timeout status, not a hang). */
 size_t sy_expert_ffn_scratch_bytes(int n_experts);
 int sy_expert_ffn(const void* x, const int32_t* a_rows, const void* gate_up, const void* down, const int32_t* begins,
                   const int32_t* ends, int n_ranges, int ranges_per_expert, int rows_bound, int hidden, int inter,
                   const void* wsorted, void* act, void* y, const uint64_t* y_table, int32_t* scratch, int dtype,
                   int compute_shape, void* stream);
+
+/* expert_ffn_combine — sy_expert_ffn in its streaming shape with sy_combine folded into the down
+ * projection's epilogue: replaces switchyard/kernels.py:56-58 and the combine that follows
+ * (l.87-88) with one launch. Rows are the plain sorted batch (offsets as from sy_sort_by_expert,
+ * token = the sort's token[], pos_of = its pos_of[], rows = n_tokens * top_k). Every result tile
+ * counts, per token and block of 128 output columns, the rows it has stored; the tile that
+ * stores a token's last row sums that token's rows in ascending row order (= ascending expert
+ * id, ties by slot: sy_combine's order) in float32 and rounds once. out [n_tokens, hidden] holds
+ * the same bits sy_combine would give; y [rows, hidden] is still written.
+ * scratch: sy_expert_ffn_combine_scratch_bytes(...) bytes, zero before the first call, left zero. */
+size_t sy_expert_ffn_combine_scratch_bytes(int n_experts, int n_tokens, int hidden);
+int sy_expert_ffn_combine(const void* x, const int32_t* token, const void* gate_up, const void* down,
+                          const int32_t* offsets, int n_experts, int rows, int hidden, int inter, const void* wsorted,
+                          void* act, void* y, const int32_t* pos_of, int top_k, int n_tokens, void* out,
+                          int32_t* scratch, int dtype, void* stream);
 
 /* combine — replaces `combine` (moe_kernels.cu:435-444, kernel l.417-433).
  * out[t, :] = round16( sum_j float(y[pos_of[t*top_k + order_j], :]) ), the token's top_k rows
@@ -171,12 +226,14 @@ int sy_copy_async(void* dst, const void* src, size_t bytes, void* stream);
  * Already-enabled is not an error. */
 int sy_enable_peer_access(int device, int peer, int* enabled_out);
 
-/* ---- expert parallelism with one process per GPU ------------------------------------------
+/* ---- expert parallelism over device-driven transport ----------------------------------------
  * The entry points below have no single counterpart in the reference: together they replace
  * the body of ExpertParallel.phase_send / phase_compute / phase_combine (switchyard/ep.py:174-272)
  * — per destination a gather_rows + three copy_async + an event, per received segment an ffn +
- * a copy back + an event — with five launches per layer that never involve the host.
- * See csrc/ep.cu for the protocol. All pointer tables are HOST arrays of device pointers. */
+ * a copy back + an event — with three launches per rank and layer that never involve the host.
+ * See csrc/ep.cu for the protocol. All pointer tables are HOST arrays of device pointers; entry
+ * i belongs to rank i. Memory of other ranks is reached by peer access (one process) or through
+ * the IPC mappings below (one process per GPU). */
 
 /* grouped_segments — sy_grouped_gemv (compute_shape = 0) or sy_grouped_gemm (1) over explicit
  * row ranges. Range g is rows [begins[g], ends[g]) of A (no gather); expert e (weights B[e])
@@ -195,53 +252,50 @@ int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, con
  * receivers' arrival flags; the other entry points of the same layer read it. The host passes
  * no per-layer value, so a whole layer can be captured in a CUDA graph and replayed. */
 
-/* ep_dispatch — sends every sorted row to the rank owning its expert: row i (expert in
- * [d*experts_per_rank, (d+1)*experts_per_rank)) is copied from h[token[i]] to row
- * i - offsets[d*experts_per_rank] of x_dst[d], its router weight to w_dst[d]; meta_dst[d] gets
- * experts_per_rank+1 rebased offsets, the segment's first row and its row count; finally
- * *flag_dst[d] = ++*epoch_counter (release, system scope) for every d. done_counter: one zero-initialised
- * int of this rank's memory. Rows past `capacity` of a mailbox are dropped and reported through
- * the status word. m == 0 still publishes (empty) mailboxes. */
-int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
-                   int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
-                   void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* done_counter,
-                   int32_t* epoch_counter, void* stream);
+/* ep_dispatch — sends every sorted row to the rank owning its expert (replaces
+ * switchyard/ep.py:193-223): row i (expert in [d*experts_per_rank, (d+1)*experts_per_rank)) is
+ * copied from h[token[i]] to row i - offsets[d*experts_per_rank] of x_dst[d], its router weight
+ * to w_dst[d]; meta_dst[d] gets experts_per_rank+1 rebased offsets, the segment's first row and
+ * its row count. As soon as everything bound for receiver d is stored, *flag_dst[d] becomes
+ * *epoch_counter + 1 (release, system scope); the last block out then advances *epoch_counter.
+ * rows_bound: the number of sorted rows as the host knows it (sizes the grid; the kernel takes
+ * the exact count from offsets; 0 still publishes empty mailboxes). counters:
+ * sy_ep_dispatch_scratch_bytes(n_ranks) bytes of this rank's memory, zero before the first call,
+ * left zero. stats: NULL, or two int64 that accumulate the rows sent to other ranks and the rows
+ * kept. Rows past `capacity` of a mailbox are dropped and reported through the status word. */
+size_t sy_ep_dispatch_scratch_bytes(int n_ranks);
+int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int rows_bound,
+                   int experts_per_rank, int n_ranks, int self_rank, int row_bytes, int capacity, void* const* x_dst,
+                   void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* counters,
+                   int32_t* epoch_counter, int64_t* stats, void* stream);
 
-/* ep_wait_build — waits (bounded, 2 s) until arrive_flags[s] >= *epoch_counter for every sender, then
- * builds the row groups of this rank's mailbox (group e*n_ranks + s = sender s's rows of local
- * expert e; sender s's rows start at s*capacity) and c_table (where each group's results go:
- * y_dst[s] + (first row of the segment in the sender's sort + rebased offset) * out_row_bytes). */
-int sy_ep_wait_build(const int32_t* arrive_flags, const int32_t* meta, int experts_per_rank, int n_ranks,
-                     int capacity, void* const* y_dst, int out_row_bytes, const int32_t* epoch_counter,
-                     int32_t* begins, int32_t* ends, uint64_t* c_table, void* stream);
+/* ep_expert_ffn — sy_expert_ffn over this rank's mailbox (replaces switchyard/ep.py:239-262: one
+ * ffn per received segment, a copy back and an event each). The kernel waits (bounded) until
+ * arrive_flags[s] >= *epoch_counter for every sender s, builds its row ranges from the senders'
+ * metadata (range e*n_ranks + s = sender s's rows of local expert e; sender s's rows start at
+ * s*capacity of x_mail / w_mail; an expert's ranges share its tiles, so its weights are read
+ * once), and the down projection's epilogue stores result row i of sender s's segment into
+ * y_dst[s] + (first row of the segment in the sender's sort + i) * hidden * 2 bytes. When the
+ * whole launch is done, *ret_flag_dst[s] = *epoch_counter (release, system scope) for every s.
+ * act: 16-bit [n_ranks*capacity, inter] scratch. scratch: as sy_expert_ffn. */
+int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const int32_t* meta, const int32_t* arrive_flags,
+                     const int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity, const void* gate_up,
+                     const void* down, int hidden, int inter, void* act, void* const* y_dst,
+                     int32_t* const* ret_flag_dst, int32_t* scratch, int dtype, int compute_shape, void* stream);
 
-/* ep_signal — *flag_dst[s] = *epoch_counter (release, system scope) for every s, after everything
- * enqueued before it on `stream` (the results written into the senders' memory) is done. */
-int sy_ep_signal(int32_t* const* flag_dst, int n_ranks, const int32_t* epoch_counter, void* stream);
+/* ep_wait — one small kernel that waits (bounded, see sy_set_wait_limit_ns) until
+ * flags[i] >= *epoch_counter + epoch_offset for i < n (n <= 32). The building block of the waits
+ * above on its own: callers that schedule the steps themselves use it, and tests use it to see a
+ * wait run out (status 5) without anything else depending on the flag. */
+int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, int epoch_offset, void* stream);
 
-/* ep_wait — waits (bounded, 2 s) until flags[i] >= *epoch_counter for i < n (n <= 32). */
-int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, void* stream);
-
-/* ep_dispatch_build — sy_ep_dispatch and sy_ep_wait_build in ONE launch: the dispatch's last
- * block, once it has published this rank's rows, waits (bounded) for every sender's arrival flag
- * and writes the row groups and the result table. Arguments: those of sy_ep_dispatch, then
- * those of sy_ep_wait_build (arrive_flags, meta, y_dst, out_row_bytes, begins, ends, c_table).
- * Replaces the same reference lines as the two (switchyard/ep.py:193-223, 239-262). */
-int sy_ep_dispatch_build(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets, int m,
-                         int experts_per_rank, int n_ranks, int row_bytes, int capacity, void* const* x_dst,
-                         void* const* w_dst, int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* done_counter,
-                         int32_t* epoch_counter, const int32_t* arrive_flags, const int32_t* meta, void* const* y_dst,
-                         int out_row_bytes, int32_t* begins, int32_t* ends, uint64_t* c_table, void* stream);
-
-/* ep_combine — sy_ep_signal, sy_ep_wait and sy_combine in ONE launch: block 0 release-stores the
- * layer's epoch into every sender's return flag (flag_dst), every block waits (bounded) until
- * all n_ranks owners have done the same for this rank (ret_flags), then sums its token's rows as
- * sy_combine does (same order, same bits; y is read with L1 bypassed, its rows were stored by
- * other GPUs while the kernel waited). A rank with n_tokens == 0 still launches one block.
+/* ep_combine — waits (bounded) until ret_flags[d] >= *epoch_counter for all n_ranks owners, then
+ * sums each token's rows as sy_combine does (same order, same bits; y is read with L1 bypassed,
+ * its rows were stored by other GPUs). A rank with n_tokens == 0 still launches one block.
  * Replaces switchyard/ep.py:264-272 followed by the combine (moe_kernels.cu:417-444). */
-int sy_ep_combine(int32_t* const* flag_dst, const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter,
-                  const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out,
-                  int dtype, void* stream);
+int sy_ep_combine(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
+                  const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out, int dtype,
+                  void* stream);
 
 /* ipc_export / ipc_open / ipc_close — map one rank's window into another process (CUDA IPC).
  * export: 64-byte handle of the allocation containing ptr and ptr's offset in it.

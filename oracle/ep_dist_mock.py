@@ -1,8 +1,8 @@
 """A host-memory stand-in for the device side of switchyard_b200.ep_dist. TEST INFRASTRUCTURE ONLY.
 
 `DistributedExpertParallel` talks to its device through a small backend object: the C-ABI entry
-points of the transport (`sy_ep_dispatch`, `sy_ep_wait_build`, `sy_grouped_segments`,
-`sy_ep_signal`, `sy_ep_wait`, `sy_ipc_*`), the routing / sort / combine wrappers, and memory.
+points of the transport (`sy_ep_dispatch`, `sy_ep_expert_ffn`, `sy_ep_combine`, `sy_ipc_*`), the
+routing and sort step, and memory.
 `MockBackend` provides the same names over HOST shared memory: a rank's window is a file in
 /dev/shm that the other processes map (the stand-in for CUDA IPC), "kernels" are numpy / torch
 code working on raw addresses, and flag waits are bounded polling loops. With it the product's
@@ -77,11 +77,14 @@ class _Lib:
         return 0
 
     # ---- transport
-    def sy_ep_dispatch(self, h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
-                       done_counter, epoch_counter, stream):
+    def sy_ep_dispatch(self, h, token, wsorted, offsets, rows_bound, per, R, self_rank, row_bytes, cap, x_dst, w_dst,
+                       meta_dst, flag_dst, counters, epoch_counter, stats, stream):
         off = _view(offsets, R * per + 1, np.int32)
+        m = int(off[R * per])
         tok = _view(token, m, np.int32) if m else np.zeros(0, np.int32)
         wsrc = _view(wsorted, m, np.int16) if m else np.zeros(0, np.int16)
+        ep = _view(epoch_counter, 1, np.int32)
+        epoch = int(ep[0]) + 1
         for d in range(R):
             a, b = int(off[d * per]), int(off[(d + 1) * per])
             n = min(b - a, cap)
@@ -94,10 +97,12 @@ class _Lib:
                 hsrc = _view(h, (int(src_rows.max()) + 1) * row_bytes, np.uint8).reshape(-1, row_bytes)
                 dst[:] = hsrc[src_rows]
                 _view(w_dst[d], n, np.int16)[:] = wsrc[a:a + n]
-        ep = _view(epoch_counter, 1, np.int32)
-        epoch = int(ep[0]) + 1
-        for d in range(R):
-            _view(flag_dst[d], 1, np.int32)[0] = epoch
+            _view(flag_dst[d], 1, np.int32)[0] = epoch  # this receiver's rows are in place
+        if _addr(stats):
+            st = _view(stats, 2, np.int64)
+            kept = int(off[(self_rank + 1) * per] - off[self_rank * per])
+            st[0] += m - kept
+            st[1] += kept
         ep[0] = epoch
         return 0
 
@@ -111,31 +116,25 @@ class _Lib:
             time.sleep(0.0005)
         return True
 
-    def sy_ep_wait_build(self, arrive_flags, meta, per, R, cap, y_dst, out_row_bytes, epoch_counter, begins, ends,
-                         c_table, stream):
-        epoch = int(_view(epoch_counter, 1, np.int32)[0])
-        if not self._wait(arrive_flags, R, epoch):
-            return -3
+    def _groups(self, meta, per, R, cap, y_dst, out_row_bytes):
+        """Row ranges and result addresses from the senders' metadata (what the expert kernel builds)."""
         m = _view(meta, R * (per + 3), np.int32).reshape(R, per + 3)
-        b, e, c = _view(begins, R * per, np.int32), _view(ends, R * per, np.int32), _view(c_table, R * per, np.uint64)
+        b, e, c = np.zeros(R * per, np.int32), np.zeros(R * per, np.int32), np.zeros(R * per, np.uint64)
         for g in range(R * per):
             ex, s = divmod(g, R)
             lo, hi = int(m[s, ex]), min(int(m[s, ex + 1]), cap)
             b[g], e[g] = s * cap + lo, s * cap + max(hi, lo)
             c[g] = int(y_dst[s]) + (int(m[s, per + 1]) + lo) * out_row_bytes
-        return 0
+        return b, e, c
 
-    def sy_grouped_segments(self, A, B, begins, ends, n_groups, groups_per_expert, rows_bound, n_out, k_dim, swiglu,
-                            scale, C, c_table, dtype, compute_shape, stream):
+    def _segments(self, A, B, b, e, per_expert, n_out, k_dim, swiglu, scale, C, table, dtype):
         dt = torch.float16 if dtype == 0 else torch.bfloat16
-        b, e = _view(begins, n_groups, np.int32), _view(ends, n_groups, np.int32)
         n_full = 2 * n_out if swiglu else n_out
-        table = _view(c_table, n_groups, np.uint64) if _addr(c_table) else None
-        for g in range(n_groups):
+        for g in range(len(b)):
             lo, hi = int(b[g]), int(e[g])
             if hi <= lo:
                 continue
-            W = _torch16(_addr(B) + (g // groups_per_expert) * n_full * k_dim * 2, n_full, k_dim, dt)
+            W = _torch16(_addr(B) + (g // per_expert) * n_full * k_dim * 2, n_full, k_dim, dt)
             x = _torch16(_addr(A) + lo * k_dim * 2, hi - lo, k_dim, dt)
             out_addr = int(table[g]) if table is not None else _addr(C) + lo * n_out * 2
             out = _torch16(out_addr, hi - lo, n_out, dt)
@@ -148,29 +147,24 @@ class _Lib:
                     out[r] = mo.epilogue_scale(acc, sc[r:r + 1], dt)[0]
                 else:
                     out[r] = acc.to(dt)[0]
+
+    def sy_ep_expert_ffn(self, x_mail, w_mail, meta, arrive_flags, epoch_counter, R, per, cap, gate_up, down, hidden,
+                         inter, act, y_dst, ret_flag_dst, scratch, dtype, compute_shape, stream):
+        epoch = int(_view(epoch_counter, 1, np.int32)[0])
+        if not self._wait(arrive_flags, R, epoch):
+            return -3
+        b, e, c = self._groups(meta, per, R, cap, y_dst, hidden * 2)
+        self._segments(x_mail, gate_up, b, e, R, inter, hidden, 1, None, act, None, dtype)
+        self._segments(act, down, b, e, R, hidden, inter, 0, w_mail, None, c, dtype)
+        for s in range(R):
+            _view(ret_flag_dst[s], 1, np.int32)[0] = epoch
         return 0
 
-    def sy_expert_ffn(self, x, a_rows, gate_up, down, begins, ends, n_ranges, per_expert, rows_bound, hidden, inter,
-                      wsorted, act, y, y_table, scratch, dtype, compute_shape, stream):
-        assert not _addr(a_rows)
-        rc = self.sy_grouped_segments(x, gate_up, begins, ends, n_ranges, per_expert, rows_bound, inter, hidden, 1, None,
-                                      act, None, dtype, compute_shape, stream)
-        return rc or self.sy_grouped_segments(act, down, begins, ends, n_ranges, per_expert, rows_bound, hidden, inter, 0,
-                                              wsorted, y, y_table, dtype, compute_shape, stream)
-
-    def sy_ep_dispatch_build(self, h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
-                             done_counter, epoch_counter, arrive_flags, meta, y_dst, out_row_bytes, begins, ends, c_table,
-                             stream):
-        rc = self.sy_ep_dispatch(h, token, wsorted, offsets, m, per, R, row_bytes, cap, x_dst, w_dst, meta_dst, flag_dst,
-                                 done_counter, epoch_counter, stream)
-        return rc or self.sy_ep_wait_build(arrive_flags, meta, per, R, cap, y_dst, out_row_bytes, epoch_counter, begins,
-                                           ends, c_table, stream)
-
-    def sy_ep_combine(self, flag_dst, ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, out, dtype,
-                      stream):
-        rc = self.sy_ep_signal(flag_dst, R, epoch_counter, stream) or self.sy_ep_wait(ret_flags, R, epoch_counter, stream)
-        if rc or n_tokens == 0:
-            return rc
+    def sy_ep_combine(self, ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, out, dtype, stream):
+        if not self._wait(ret_flags, R, int(_view(epoch_counter, 1, np.int32)[0])):
+            return -3
+        if n_tokens == 0:
+            return 0
         dt = torch.float16 if dtype == 0 else torch.bfloat16
         m = n_tokens * top_k
         pos = torch.from_numpy(_view(pos_of, m, np.int32).copy())
@@ -180,14 +174,8 @@ class _Lib:
         _torch16(_addr(out), n_tokens, hidden, dt).copy_(mo.combine_expert_order(yy, pos, ix, n_tokens))
         return 0
 
-    def sy_ep_signal(self, flag_dst, R, epoch_counter, stream):
-        epoch = int(_view(epoch_counter, 1, np.int32)[0])
-        for s in range(R):
-            _view(flag_dst[s], 1, np.int32)[0] = epoch
+    def sy_device_status(self, stream, out):
         return 0
-
-    def sy_ep_wait(self, flags, n, epoch_counter, stream):
-        return 0 if self._wait(flags, n, int(_view(epoch_counter, 1, np.int32)[0])) else -3
 
 
 class _Ext:
@@ -238,6 +226,13 @@ class MockBackend:
 
     def linear(self, h, router):
         return torch.stack([_row_linear(r, router) for r in h]).to(h.dtype) if h.shape[0] else h.new_zeros(0, router.shape[0])
+
+    def route_and_sort(self, h, router, k, norm, bias):
+        logits = self.linear(h, router)
+        if bias is not None:
+            logits = logits + bias
+        idx, w = mo.route_kernel_rule(logits, k, norm)
+        return [idx, w] + list(mo.sort_by_expert(idx, w, router.shape[0]))
 
     def stream(self):
         return _NullStream()

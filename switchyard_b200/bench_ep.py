@@ -41,6 +41,25 @@ def rank_weights(device, dtype, seed, lo, hi):
     return router, gate_up, down
 
 
+def check_bit_identity(ep, kernels, layer, full, hs, rank, world):
+    """Every rank's expert-parallel output against the single-GPU layer on the same tokens with
+    the whole expert set (same mode): must be the same bits. Collective; returns (ok on every
+    rank, rows each rank sent / kept during the check)."""
+    ok = True
+    for h in hs:
+        got = ep.layer(h, *layer)
+        want = kernels.moe_layer_with_bias(h, full[0], full[1], full[2], TOPK, False, ep.mode, ep.bias)
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.equal(got, want))
+    verdict = torch.tensor([1 if ok else 0], device=hs[0].device)
+    dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    sent, kept = ep.row_counts()
+    rows = torch.zeros(world, 2, dtype=torch.int64, device=hs[0].device)
+    rows[rank, 0], rows[rank, 1] = sent, kept
+    dist.all_reduce(rows)
+    return bool(int(verdict)), rows.tolist()
+
+
 def run(args):
     from . import kernels, synthetic
     from .ep_dist import DistributedExpertParallel
@@ -56,6 +75,16 @@ def run(args):
     layers = [rank_weights(dev, dtype, 100 + l, rank * per, (rank + 1) * per) for l in range(LAYERS)]
     hs = {T: synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T) for T in SWEEP}
     ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=max(SWEEP), dtype=dtype, mode=mode, device=dev)
+    # before anything is timed: the expert-parallel layer must give the single-GPU layer's bits
+    full = synthetic.layer_weights(dev, dtype, seed=100)
+    identical, check_rows = check_bit_identity(ep, kernels, layers[0], full, [hs[T] for T in SWEEP], rank, world)
+    del full
+    torch.cuda.empty_cache()
+    if not identical:
+        if rank == 0:
+            print(json.dumps({"error": "expert-parallel output differs from the single-GPU layer", "n_gpus": world}), flush=True)
+        dist.destroy_process_group()
+        raise SystemExit(1)
 
     # experts used per (T, layer) over ALL ranks' tokens: fixed by the seeds; for the byte count
     used = {}
@@ -169,12 +198,15 @@ def run(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "configs[1] decode sweep T=1,8,32,64 tokens PER GPU, fp16, expert-parallel: "
-                                   f"{per} experts per GPU, P2P dispatch and return; a step = one layer at each T",
-                       "tokens_per_gpu": list(SWEEP), "hidden": H, "expert_width": I, "experts": E, "top_k": TOPK,
-                       "mode": mode, "parallelism": f"ep{world} (attention data-parallel)",
-                       "l2": f"passes rotate over {LAYERS} resident weight sets",
-                       "timing": "CUDA events on each rank's stream around CUDA-graph replays of the whole layer, max over ranks"},
+            "config": bench.CONFIG,
+            "arm": {"mode": mode, "parallelism": f"ep{world}: {per} experts per GPU, T tokens PER GPU (weak scaling in "
+                                                 "tokens), attention data-parallel; dispatch and return by kernels "
+                                                 "writing into peer memory, no collective on the data path",
+                    "timing": "CUDA events on each rank's stream around CUDA-graph replays of the whole layer, max over ranks"},
+            "ep_bit_identical": identical,
+            "ep_check": {"what": "every rank's layer output == kernels.moe_layer on its own tokens with all 64 experts, "
+                                 "T=1,8,32,64, torch.equal, before timing",
+                         "rows_sent_kept_per_rank": check_rows},
             "sweep": [{"tokens_per_gpu": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
                        "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
                        "tokens_per_s": T * world * args.steps / (per_T_ms[T] / 1e3)} for T in SWEEP],
@@ -182,9 +214,8 @@ def run(args):
             "e2e": {"value": e2e_bytes / (float(e2e_t) / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                     "d2h_bytes_per_step": io_bytes, "ms_per_step": float(e2e_t) / args.steps,
                     "api": "switchyard_b200.ep_dist.DistributedExpertParallel.layer, host buffers pinned"},
-            # this library's kernels per layer and rank: route (+ sort: one launch up to 16 tokens),
-            # dispatch+build, expert FFN, signal+wait+combine; the cuBLAS router GEMM is not counted
-            "gpu_launches": args.steps * sum(4 if T <= kernels.ROUTE_SORT_MAX_TOKENS else 5 for T in SWEEP) * world,
+            # this library's kernels per layer and rank: route_fused, dispatch, expert FFN, combine
+            "gpu_launches": args.steps * 4 * len(SWEEP) * world,
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_source": peak_src,
                          "kernel": "whole expert-parallel layer, per GPU (the weight-stream kernel is profiled at N=1)"},
@@ -223,6 +254,12 @@ def run_config(args):
             m = kernels.auto_mode(T * world * TOPK, E)
             ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode=m, device=dev,
                                            logit_bias=bias)
+            full = synthetic.layer_weights(dev, dtype, seed=100)
+            identical, rows_rank = check_bit_identity(ep, kernels, layers[0], full, [h], rank, world)
+            del full
+            torch.cuda.empty_cache()
+            if not identical:
+                raise SystemExit(f"rank {rank}: expert-parallel output differs from the single-GPU layer at T={T}")
             run = lambda l: ep.layer(h, *layers[l])
             mode_used = m
         else:
@@ -230,9 +267,9 @@ def run_config(args):
 
             def run(l):
                 router, gu, dn = layers[l]
-                idx, w = kernels.ext().route((torch.nn.functional.linear(h, router) + b).contiguous(), TOPK, False)
-                return kernels.experts(h, idx, w, gu, dn, mode)
+                return kernels.moe_layer_with_bias(h, router, gu, dn, TOPK, False, mode, b)
             mode_used = mode
+            identical, rows_rank = None, None
         stream = torch.cuda.Stream(dev)
         with torch.cuda.stream(stream):
             for i in range(max(args.warmup, 3)):
@@ -270,7 +307,8 @@ def run_config(args):
         rows = T * world * TOPK
         out.append({"tokens_per_gpu": T, "ms_per_layer": ms, "tokens_per_s": T * world / (ms / 1e3),
                     "tflops": rows * 12582912 / (ms / 1e3) / 1e12, "tflops_per_gpu": rows * 12582912 / (ms / 1e3) / 1e12 / world,
-                    "mode": mode_used, "busiest_over_mean": skew})
+                    "mode": mode_used, "busiest_over_mean": skew, "ep_bit_identical": identical,
+                    "rows_sent_kept_per_rank": rows_rank})
     if rank == 0:
         print(json.dumps({"config": args.config, "n_gpus": world, "dtype": str(dtype).replace("torch.", ""),
                           "steps": args.steps, "timing": "CUDA events around CUDA-graph replays of the whole layer, max over ranks",

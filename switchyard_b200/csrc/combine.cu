@@ -15,7 +15,7 @@ combine_kernel(const T* __restrict__ y, const int* __restrict__ pos_of, const in
   __shared__ int s_row[COMBINE_MAX_K];
   pdl_launch_dependents();
   pdl_wait();  // y comes from the down projection before this kernel
-  combine_token<T, false>(y, pos_of, idx, k, H, out, blockIdx.x, s_row);
+  combine_token<T, false>(y, pos_of, idx, k, H, out, blockIdx.x, s_row, (int)gridDim.x * k);
 }
 
 }  // namespace sy

@@ -11,10 +11,12 @@ constexpr int COMBINE_MAX_K = 8;
 // Token t's top-k rows of y summed in float32 in ascending expert order (ties by slot), rounded
 // once. The whole block works on one token; s_row is COMBINE_MAX_K ints of shared memory.
 // COHERENT: read y with L1 bypassed (rows that another GPU stored while this kernel ran).
+// A choice without a row (pos_of outside [0, m): the sort skipped an invalid expert id) adds
+// nothing.
 template <typename T, bool COHERENT>
 __device__ __forceinline__ void combine_token(const T* __restrict__ y, const int* __restrict__ pos_of,
                                               const int* __restrict__ idx, int k, int H, T* __restrict__ out, int t,
-                                              int* s_row) {
+                                              int* s_row, int m) {
   if (threadIdx.x < k) {
     // rank of this slot among the token's k choices by (expert id, slot)
     int e = idx[(size_t)t * k + threadIdx.x], rank = 0;
@@ -22,7 +24,8 @@ __device__ __forceinline__ void combine_token(const T* __restrict__ y, const int
       int ej = idx[(size_t)t * k + j];
       rank += (ej < e) || (ej == e && j < (int)threadIdx.x);
     }
-    s_row[rank] = pos_of[(size_t)t * k + threadIdx.x];
+    const int pos = pos_of[(size_t)t * k + threadIdx.x];
+    s_row[rank] = pos >= 0 && pos < m ? pos : -1;
   }
   __syncthreads();
   const int chunks = H >> 3;
@@ -31,8 +34,11 @@ __device__ __forceinline__ void combine_token(const T* __restrict__ y, const int
 #pragma unroll
     for (int j = 0; j < COMBINE_MAX_K; ++j)
       if (j < k) {
-        const uint4* p = reinterpret_cast<const uint4*>(y + (size_t)s_row[j] * H) + c;
-        v[j] = COHERENT ? __ldcg(p) : __ldg(p);
+        v[j] = make_uint4(0u, 0u, 0u, 0u);  // sixteen-bit zeros: adds nothing
+        if (s_row[j] >= 0) {
+          const uint4* p = reinterpret_cast<const uint4*>(y + (size_t)s_row[j] * H) + c;
+          v[j] = COHERENT ? __ldcg(p) : __ldg(p);
+        }
       }
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll

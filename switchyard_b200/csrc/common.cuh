@@ -19,6 +19,7 @@ int check_cuda(cudaError_t e, const char* what);
 int device_sm_count(int* out);           // SMs of the current device (cached per device)
 int current_device_slot(int* out);       // current device ordinal, < SY_MAX_DEVICES
 int* device_status_word();               // device address of this device's kernel status word
+uint64_t wait_limit_ns();                // how long kernels wait for a flag or barrier before giving up
 
 #define SY_CUDA(expr)                                           \
   do {                                                          \
@@ -192,6 +193,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
   }
 }
 
+// ---- flags between GPUs ---------------------------------------------------------------------
+// A flag is an int in one GPU's memory that another GPU's kernel release-stores an ever-growing
+// epoch into; the owner's kernels wait until it has reached the epoch they expect.
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until *flag >= epoch; gives up (false) after limit_ns.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t limit_ns) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (ld_acquire_sys(flag) >= epoch) return true;
+    if ((spin & 31u) == 0) {
+      if (global_timer_ns() - start > limit_ns) return false;
+      __nanosleep(100);
+    }
+  }
+}
+
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -256,6 +281,33 @@ __device__ __forceinline__ void st_global_32(void* p, const uint32_t (&v)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]),
                "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
                : "memory");
+}
+
+// One 16-bit element read through L2 (written by another block of the same launch).
+template <typename T> __device__ __forceinline__ T ldcg16(const T* p) {
+  unsigned short v;
+  asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return reinterpret_cast<T&>(v);
+}
+
+// Warp-level 16x8x16 matrix multiply-accumulate (16-bit inputs, float32 accumulators): the small
+// router GEMM of the fused routing kernel. The expert FFN does not use it.
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // ---- tcgen05 / tensor memory --------------------------------------------------------------

@@ -46,21 +46,6 @@
 
 namespace sy {
 
-// Profiling build only (-DSY_PROFILE, not part of the shipped library): blocks 0 and 1 add up
-// the clocks each role spends waiting and working; sy_prof_read returns the totals.
-#ifdef SY_PROFILE
-__device__ unsigned long long g_prof[32];
-#define PROF_T0 long long prof_t = clock64()
-#define PROF_ADD(i)                                                                       \
-  do {                                                                                    \
-    const long long prof_n = clock64();                                                   \
-    if (blockIdx.x < 2) atomicAdd(&g_prof[blockIdx.x * 16 + (i)], (unsigned long long)(prof_n - prof_t)); \
-    prof_t = prof_n;                                                                      \
-  } while (0)
-#else
-#define PROF_T0
-#define PROF_ADD(i)
-#endif
 
 constexpr int GM_ATOM_K = 64;                      // k per swizzle atom: 128-byte rows
 constexpr int GM_BM = 128;                         // weight rows per accumulator (UMMA M)
@@ -76,7 +61,8 @@ constexpr int GM_MAX_BN = 256;                      // most token rows in a tile
 constexpr int GM_EPI_ROWS = 64;                    // token rows the epilogue stages per pass
 constexpr int GM_EPI_BYTES = GM_EPI_ROWS * GM_BM * 2;  // staged output tile: 64 rows x 128 columns
 constexpr int GM_SMEM = GM_RING_BYTES + GM_EPI_BYTES + 1024;  // + room to align the ring to 1024
-constexpr uint64_t GM_WAIT_NS = 1000000000ull;
+constexpr int GM_MAX_RANKS = 16;                   // ranks of an expert-parallel group
+constexpr int COMBINE_K = 8;                       // most choices per token the fused combine handles
 
 // Three shapes of the same kernel.
 //   SH_STREAM (mode "gemv"): the weight tile is the MMA's M operand (128 weight rows; with
@@ -126,20 +112,52 @@ struct Problem {
   const int* a_rows;
   const void* scale;
   void* C;
-  const unsigned long long* c_table;     // optional per-range output row pointers
+  int use_table;                         // results go through the table of per-range row pointers
   int Nout, K, swiglu;
   int x_tma;                             // A's rows are the ranges' rows themselves (no a_rows, one range per
                                          // expert): a tile's rows are contiguous and come by TMA, not by gather
+};
+
+// Expert-parallel mode (arrive != nullptr). The rows sit in this rank's mailbox, one slot of `cap`
+// rows per sender. The kernel itself waits (bounded) for every sender's arrival flag, reads the
+// senders' metadata (meta[s] = per + 1 rebased offsets | first row in the sender's sort | rows),
+// builds the row ranges (range e * R + s = sender s's rows of local expert e) and the table of
+// where each range's results go (into the SENDER's result buffer, at the rows its own sort gave
+// them), and when its last result tile has been stored it release-stores the layer's epoch into
+// every sender's return flag.
+struct EpArgs {
+  const int* arrive;
+  const int* meta;
+  const int* epoch_counter;
+  int R, per, cap, out_row_bytes;
+  unsigned char* y[GM_MAX_RANKS];
+  int* ret_flag[GM_MAX_RANKS];
+};
+
+// Combine fused into the last problem's epilogue (streaming shape, local results): every result
+// tile counts, per token and column block, the rows of that token it has stored; whoever stores
+// a token's last row sums the token's rows of that column block in ascending row order (which is
+// ascending expert order, the combine kernel's order) and writes the layer's output.
+struct CombineArgs {
+  void* out;                             // [n_tokens, Nout]; nullptr: no combine
+  const int* token;                      // [rows] token of each sorted row
+  const int* pos_of;                     // [n_tokens * k] sorted row of each choice
+  int* arrivals;                         // [n_tokens * column blocks] zero before and after the launch
+  int k, rows;
 };
 
 struct KernelArgs {
   Problem p[2];
   const int* begins;                     // [ranges]
   const int* ends;
+  const unsigned long long* c_table;     // [ranges] optional per-range output row pointers
   int ranges, group_div;                 // expert e owns ranges [e*group_div, (e+1)*group_div)
   int n_problems;                        // 1, or 2 = fused FFN: p[1] reads what p[0] wrote
-  int* ready;                            // fused only: [experts] finished p[0] tiles, then [1] block counter
+  int* ready;                            // fused: [experts] finished p[0] tiles, then [1] blocks that have left
   int* status;
+  unsigned long long wait_ns;            // limit of every wait in the kernel
+  EpArgs ep;
+  CombineArgs cmb;
 };
 
 // Rows come in ranges [begin, end). Normally an expert has one range: its slice of the sorted
@@ -407,6 +425,86 @@ __device__ __forceinline__ void epilogue_rows(const Tile& tile, int buf, uint32_
   }
 }
 
+// Sorts eight ints ascending with a fixed network of compare-exchanges (registers only).
+__device__ __forceinline__ void sort8(int (&v)[8]) {
+#define SY_CSWAP(a, b)            \
+  {                               \
+    const int lo = min(v[a], v[b]); \
+    v[b] = max(v[a], v[b]);       \
+    v[a] = lo;                    \
+  }
+  SY_CSWAP(0, 1) SY_CSWAP(2, 3) SY_CSWAP(4, 5) SY_CSWAP(6, 7)
+  SY_CSWAP(0, 2) SY_CSWAP(1, 3) SY_CSWAP(4, 6) SY_CSWAP(5, 7)
+  SY_CSWAP(1, 2) SY_CSWAP(5, 6) SY_CSWAP(0, 4) SY_CSWAP(3, 7)
+  SY_CSWAP(1, 5) SY_CSWAP(2, 6)
+  SY_CSWAP(1, 4) SY_CSWAP(3, 6)
+  SY_CSWAP(2, 4) SY_CSWAP(3, 5)
+  SY_CSWAP(3, 4)
+#undef SY_CSWAP
+}
+
+// Combine fused into the streaming shape's last epilogue. Called by the four epilogue warps
+// after they have stored a result tile (nvalid rows x up to 128 columns of y). Every row's
+// thread counts the row for its (token, column block); the thread that brings the count to the
+// number of rows the token has finishes the token for this column block: the token's rows,
+// read back through L2, summed in float32 in ascending row order (rows are sorted by expert, so
+// this is the order of the combine kernel: expert id, ties by slot) and rounded once.
+template <typename T>
+__device__ __forceinline__ void epilogue_combine(const Tile& tile, int et, int row_base, int Nout, int colbase,
+                                                 const CombineArgs& cb, const T* __restrict__ y, int col_blocks,
+                                                 int* s_final, int* s_nfinal) {
+  const int k = cb.k, rows = cb.rows;
+  if (et == 0) *s_nfinal = 0;
+  named_barrier_sync(3, GM_EPI_WARPS * 32);  // every warp's stores of this tile have been issued
+  if (et < tile.nvalid) {
+    const int t = cb.token[row_base + et];
+    int have = 0;  // rows this token has (choices that the sort gave a row)
+    for (int j = 0; j < k; ++j) {
+      const int p = cb.pos_of[(size_t)t * k + j];
+      have += p >= 0 && p < rows;
+    }
+    __threadfence();
+    int* counter = cb.arrivals + (size_t)t * col_blocks + tile.cb;
+    if (atomicAdd(counter, 1) + 1 == have) {
+      *counter = 0;  // nobody else touches it in this launch; the next launch finds zero
+      __threadfence();
+      s_final[atomicAdd(s_nfinal, 1)] = t;
+    }
+  }
+  named_barrier_sync(3, GM_EPI_WARPS * 32);
+  const int nfinal = *s_nfinal;
+  const int chunk = et & 15, lane8 = et >> 4;  // sixteen 16-byte chunks per 128 columns; eight tokens at a time
+  const int col = colbase + chunk * 8;
+  if (col >= Nout) return;
+  for (int f = lane8; f < nfinal; f += GM_EPI_WARPS * 32 / 16) {
+    const int t = s_final[f];
+    int pos[COMBINE_K];
+#pragma unroll
+    for (int j = 0; j < COMBINE_K; ++j) {
+      const int p = j < k ? cb.pos_of[(size_t)t * k + j] : -1;
+      pos[j] = p >= 0 && p < rows ? p : 0x7fffffff;
+    }
+    sort8(pos);
+    uint4 v[COMBINE_K];
+#pragma unroll
+    for (int j = 0; j < COMBINE_K; ++j)
+      if (pos[j] != 0x7fffffff) v[j] = __ldcg(reinterpret_cast<const uint4*>(y + (size_t)pos[j] * Nout + col));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < COMBINE_K; ++j)
+      if (pos[j] != 0x7fffffff) {
+        float fv[8];
+        unpack8<T>(v[j], fv);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += fv[q];
+      }
+    __align__(16) T r[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) r[q] = Elem<T>::from_f(acc[q]);
+    *reinterpret_cast<uint4*>(static_cast<T*>(cb.out) + (size_t)t * Nout + col) = *reinterpret_cast<const uint4*>(r);
+  }
+}
+
 template <typename T, int SH>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_constant__ KernelArgs args) {
   using S = Shape<SH>;
@@ -418,9 +516,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
-#ifdef SY_PROFILE
-  __shared__ long long s_issue_clock[STAGES];
-#endif
   __shared__ int s_begin[GM_MAX_E];       // row ranges
   __shared__ int s_end[GM_MAX_E];
   __shared__ int s_rows[GM_MAX_E];        // rows per expert (all its ranges)
@@ -428,12 +523,17 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ int s_map_row[2][GM_MAX_BN];  // per accumulator buffer: the tile's rows in A / C space
   __shared__ int s_map_grp[2][GM_MAX_BN];  // ... and the range each row belongs to
   __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (one-accumulator SwiGLU)
+  __shared__ unsigned long long s_ctab[GM_MAX_E];  // per-range output row pointers (given, or built in expert-parallel mode)
+  __shared__ int s_flag_ok;
+  __shared__ int s_final[GM_MAX_BN];       // fused combine: tokens this tile completes
+  __shared__ int s_nfinal;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char* stages =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* out_tile = stages + GM_RING_BYTES;  // the epilogue's staged output rows
   int* status = args.status;
+  const uint64_t GM_WAIT_NS = args.wait_ns;
   const int E = args.ranges, group_div = args.group_div, NP = args.n_problems;
   const int EL = E / group_div;  // experts; E counts row ranges
   // DUO: the two CTAs of a cluster share every tile; `unit` numbers the clusters.
@@ -482,10 +582,35 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
     }
   }
   pdl_wait();  // row ranges, activations, scale: all written by earlier kernels
-  for (int i = threadIdx.x; i < E; i += GM_THREADS) {
-    const int b = args.begins[i], e = args.ends[i];
-    s_begin[i] = b;
-    s_end[i] = e > b ? e : b;
+  if (args.ep.arrive) {
+    // expert-parallel: wait for every sender's rows, then build the ranges and the result table
+    const int R = args.ep.R, per = args.ep.per, cap = args.ep.cap;
+    if (threadIdx.x == 0) s_flag_ok = 1;
+    __syncthreads();
+    const int epoch = *args.ep.epoch_counter;
+    if ((int)threadIdx.x < R && !wait_flag(args.ep.arrive + threadIdx.x, epoch, GM_WAIT_NS)) {
+      *status = DS_TIMEOUT_FLAG;
+      s_flag_ok = 0;
+    }
+    __syncthreads();
+    const bool ok = s_flag_ok != 0;
+    for (int g = threadIdx.x; g < E; g += GM_THREADS) {
+      const int e = g / R, s = g - e * R;
+      const volatile int* m = args.ep.meta + s * (per + 3);  // written by another GPU: no cached read
+      const int lo = ok ? m[e] : 0, hi = ok ? min(m[e + 1], cap) : 0;
+      s_begin[g] = s * cap + lo;
+      s_end[g] = s * cap + (hi > lo ? hi : lo);
+      s_ctab[g] = reinterpret_cast<unsigned long long>(args.ep.y[s]) +
+                  (unsigned long long)((ok ? m[per + 1] : 0) + lo) * (unsigned long long)args.ep.out_row_bytes;
+    }
+    fence_proxy_async_all();  // the mailbox rows were written by plain (remote) stores; TMA may read them next
+  } else {
+    for (int i = threadIdx.x; i < E; i += GM_THREADS) {
+      const int b = args.begins[i], e = args.ends[i];
+      s_begin[i] = b;
+      s_end[i] = e > b ? e : b;
+      if (args.c_table) s_ctab[i] = args.c_table[i];
+    }
   }
   __syncthreads();
   if (warp == 0) {  // rows per expert and, per problem, the exclusive prefix of tiles per expert
@@ -518,9 +643,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   if (DUO) cluster_sync_all();  // the other CTA's barriers exist before anything arrives on them
   tc_fence_after_sync();
   const uint32_t tmem = s_tmem;
-#ifdef SY_PROFILE
-  const long long prof_start = clock64();
-#endif
   const int tiles0 = s_tile_start[0][EL];
   const int total_tiles = tiles0 + (NP > 1 ? s_tile_start[1][EL] : 0);
   // token rows of a STREAM tile's MMA: a multiple of 16
@@ -556,12 +678,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
                        : kind == 1 ? atom * S::W_ATOM_BYTES + S::BOX_ROWS * 128
                                    : S::W_BYTES + atom * S::X_ATOM_BYTES;
       // One stage: lane 0 waits for the slot and announces the bytes, then every box is issued by
-      // its lane.
-      auto issue_stage = [&](int kb, int g) -> bool {
+      // its lane. `boxes`: 3 = the whole stage; 1 = claim the slot, announce the whole stage's
+      // bytes, send only the weight boxes; 2 = only the token box of a stage claimed earlier.
+      auto issue_stage = [&](int kb, int g, int boxes) -> bool {
         const int s = g % STAGES, use = g / STAGES;
-        PROF_T0;
         int ok = 1;
-        if (lane == 0) {
+        if (lane == 0 && (boxes & 1)) {
           if (use > 0) ok = (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS);
           // DUO: both CTAs' bytes are counted on the leader's barrier
           if (ok && cr == 0) mbar_arrive_expect_tx(&full_bar[s], S::CTAS * stage_bytes);
@@ -571,26 +693,30 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           if (lane == 0) *status = DS_TIMEOUT_EMPTY;
           return false;
         }
-        if (lane == 0) PROF_ADD(3);
-#ifdef SY_PROFILE
-        if (lane == 0) s_issue_clock[s] = clock64();
-#endif
-        if (has_box) {
+        if (has_box && (boxes & (kind < 2 ? 1 : 2))) {
           unsigned char* dst = stages + (size_t)s * STAGE_BYTES + boff;
           const int kx = kb * S::BK + atom * GM_ATOM_K;
           if (DUO) tma_load_2d_pair(dst, map, kx, by, cluster_map(&full_bar[s], 0));
           else if (STREAM && kind < 2) tma_load_2d_hint(dst, map, kx, by, &full_bar[s], policy);
           else tma_load_2d(dst, map, kx, by, &full_bar[s]);
         }
-        if (lane == 0) PROF_ADD(4);
         return true;
       };
+      int ahead = 0;  // stages of this tile whose weight boxes are already on their way
       if (tile.phase == 1 && P.x_tma) {
         // fused FFN: the token rows are what the expert's gate/up tiles wrote. Wait (bounded) until
         // all of them have been stored; they sit earlier in every block's tile list and their own
-        // loads are already in flight, so nothing here holds them up. (Sending this tile's weight
-        // boxes ahead of the wait was measured: it takes bandwidth from the gate/up tiles that the
-        // wait is for, and the layer got 6% slower at 64 tokens.)
+        // loads are already in flight, so nothing here holds them up.
+        // When every gate/up tile of the launch runs in the first round (a handful of tokens: at
+        // most one tile per block), HBM is far from busy and this tile's weights do not depend on
+        // the wait: their boxes go out first, the token boxes follow after the wait. With more
+        // tiles than blocks that was measured to hurt (the early weights take bandwidth from the
+        // gate/up tiles the wait is for: 6 % slower at 64 tokens), so it is not done there.
+        if (STREAM && tiles0 <= units) {
+          ahead = min(STAGES, k_blocks);
+          for (int j = 0; j < ahead && alive; ++j) alive = issue_stage(j, it + j, 1);
+          if (!alive) break;
+        }
         const int need = ((s_rows[tile.e] + BN - 1) / BN) * col_blocks_of(0) * S::CTAS;
         int ok = 1;
         if (lane == 0 && ld_acquire_gpu(args.ready + tile.e) < need) {
@@ -608,8 +734,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           break;
         }
         fence_proxy_async_all();  // they were written by plain stores; TMA reads them next
+        for (int j = 0; j < ahead; ++j) issue_stage(j, it + j, 2);
+        it += ahead;
       }
-      for (int kb = 0; kb < k_blocks && alive; ++kb, ++it) alive = issue_stage(kb, it);
+      for (int kb = ahead; kb < k_blocks && alive; ++kb, ++it) alive = issue_stage(kb, it, 3);
     }
     if (!alive && cr == 0 && lane == 0)  // let the copies already issued land before the block can exit
       for (int j = it > STAGES ? it - STAGES : 0; j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1, 10000000ull);
@@ -627,7 +755,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
         const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
         const int k_blocks = k_blocks_of(tile.phase);
         const int buf = tile_no & 1, use_t = tile_no >> 1;
-        PROF_T0;
         if (use_t > 0) {
           const bool ok = DUO ? mbar_wait_cluster(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS)
                               : mbar_wait(&acc_empty[buf], (use_t - 1) & 1, GM_WAIT_NS);
@@ -638,7 +765,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           }
           tc_fence_after_sync();
         }
-        PROF_ADD(2);
         const uint32_t idesc = umma_idesc(fmt, DUO ? 2 * GM_BM : GM_BM, STREAM ? n_mma_of(tile.nvalid) : 2 * GM_BM);
         const uint32_t d = tmem + buf * S::BUF_COLS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -651,13 +777,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
             break;
           }
           tc_fence_after_sync();
-          PROF_ADD(0);
-#ifdef SY_PROFILE
-          if (blockIdx.x < 2) {  // slot 11: clocks from a stage's issue to its use; slot 12: stages
-            atomicAdd(&g_prof[blockIdx.x * 16 + 11], (unsigned long long)(clock64() - s_issue_clock[s]));
-            atomicAdd(&g_prof[blockIdx.x * 16 + 12], 1ull);
-          }
-#endif
           const uint32_t lo = ring_lo + s * (STAGE_BYTES >> 4);  // descriptor low word of the stage's first tile
 #pragma unroll
           for (int ks = 0; ks < S::BK / 16; ++ks) {
@@ -672,7 +791,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           // the stage is free once these MMAs have read it
           if (DUO) umma_commit_pair(&empty_bar[s], 3);
           else umma_commit(&empty_bar[s]);
-          PROF_ADD(1);
         }
         if (alive) {
           if (DUO) umma_commit_pair(&acc_full[buf], 3);
@@ -748,7 +866,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       const int iters = P.x_tma ? 0 : (mine + RPI - 1) / RPI;  // rows that come by TMA need no copies here
       for (int kb = first_kb; kb < k_blocks; kb += STAGES) {
         const int g = it0 + kb, s = g % STAGES, use = g / STAGES;
-        PROF_T0;
         if (use > 0) {
           int ok = lane == 0 ? (int)mbar_wait(&empty_bar[s], (use - 1) & 1, GM_WAIT_NS) : 1;
           ok = __shfl_sync(0xffffffffu, ok, 0);  // also orders the other lanes' copies after the wait
@@ -758,7 +875,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
             break;
           }
         }
-        if (gw == 0 && lane == 0) PROF_ADD(5);
         unsigned char* x = stages + (size_t)s * STAGE_BYTES + S::W_BYTES;
         const bool in_k = kb * S::BK + c * 8 < K;  // beyond K: zero fill
         const size_t koff = in_k ? (size_t)kb * S::BK : 0;
@@ -774,7 +890,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           }
         }
         cp_async_commit();
-        if (gw == 0 && lane == 0) PROF_ADD(6);
         cp_async_wait<0>();
         fence_proxy_async_smem();
         __syncwarp();
@@ -782,7 +897,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           if (DUO) mbar_arrive_cluster(cluster_map(&full_bar[s], 0));
           else mbar_arrive(&full_bar[s]);
         }
-        if (gw == 0 && lane == 0) PROF_ADD(7);
       }
     }
     }  // gather_on
@@ -801,15 +915,13 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       const bool swiglu = P.swiglu != 0;
       const T* scale = static_cast<const T*>(P.scale);
       T* C = static_cast<T*>(P.C);
-      const unsigned long long* c_table = P.c_table;
+      const unsigned long long* c_table = P.use_table ? s_ctab : nullptr;
       const int buf = tile_no & 1, use_t = tile_no >> 1;
-      PROF_T0;
       if (alive && !mbar_wait(&acc_full[buf], use_t & 1, GM_WAIT_NS)) {
         *status = DS_TIMEOUT_MMA;
         alive = false;
       }
       tc_fence_after_sync();
-      if (et == 0) PROF_ADD(8);
       if constexpr (STREAM) {
         if (swiglu)
           epilogue_stream<T, true, false>(tile, buf, tmem, q, lane, et, alive, chunk_no, Nout, colbase, scale, C, c_table,
@@ -833,7 +945,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (et == 0) PROF_ADD(9);
       if (lane == 0 && alive) {
         if (DUO) mbar_arrive_cluster(cluster_map(&acc_empty[buf], 0));
         else mbar_arrive(&acc_empty[buf]);
@@ -848,15 +959,17 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
           atomicAdd(args.ready + tile.e, 1);
         }
       }
+      if constexpr (STREAM) {
+        if (args.cmb.out && tile.phase == NP - 1)
+          epilogue_combine<T>(tile, et, s_begin[tile.e * group_div] + tile.row0, Nout, colbase, args.cmb,
+                              static_cast<const T*>(P.C), col_blocks_of(tile.phase), s_final, &s_nfinal);
+      }
     }
   }
 
   // every role ends here; tensor memory goes back before the block exits
   tc_fence_before_sync();
   __syncthreads();
-#ifdef SY_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x < 2) atomicAdd(&g_prof[blockIdx.x * 16 + 10], (unsigned long long)(clock64() - prof_start));
-#endif
   if (DUO) cluster_sync_all();  // neither CTA leaves while the other may still signal or read it
   if (warp == 1) {
     tc_fence_after_sync();
@@ -864,11 +977,21 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
     else tmem_dealloc(tmem, S::TMEM_COLS);
   }
   if (NP > 1 && threadIdx.x == 0) {
-    // fused FFN: the last block out clears the per-expert counters for the next launch
-    __threadfence();
+    // fused FFN: the last block out clears the per-expert counters for the next launch. In
+    // expert-parallel mode it also tells every sender that its results are in place: every
+    // block's result stores (into the senders' memory) precede its count here, behind a
+    // system-scope fence, and by now no block reads the mailboxes or their metadata any more.
+    if (args.ep.arrive) __threadfence_system();
+    else __threadfence();
     if (atomicAdd(args.ready + EL, 1) == (int)gridDim.x - 1) {
       for (int e = 0; e <= EL; ++e) args.ready[e] = 0;
-      __threadfence();
+      if (args.ep.arrive) {
+        __threadfence_system();
+        const int epoch = *args.ep.epoch_counter;
+        for (int r = 0; r < args.ep.R; ++r) st_release_sys(args.ep.ret_flag[r], epoch);
+      } else {
+        __threadfence();
+      }
     }
   }
 }
@@ -935,7 +1058,7 @@ struct ProblemDesc {
   int n_out, k_dim, swiglu;
   const void* scale;
   void* C;
-  const unsigned long long* c_table;
+  int use_table;           // results go through GroupedArgs::c_table (or the table built in expert-parallel mode)
 };
 
 struct GroupedArgs {
@@ -943,13 +1066,57 @@ struct GroupedArgs {
   int n_problems;
   const int32_t* begins;   // [ranges] first row of each range
   const int32_t* ends;     // [ranges] one past its last row
+  const unsigned long long* c_table;
   int ranges;              // number of row ranges (experts x ranges per expert)
   int group_div;           // ranges per expert: ranges [e*group_div, (e+1)*group_div) are expert e's rows
   int32_t* ready;          // fused FFN scratch: experts + 1 ints, zero before the first launch
   int rows;                // upper bound of the row indices in begins / ends
   int dtype;
+  EpArgs ep;               // ep.arrive != nullptr: expert-parallel mode
+  CombineArgs cmb;         // cmb.out != nullptr: combine fused into the last epilogue
   cudaStream_t stream;
 };
+
+// The grid is persistent and its blocks wait on one another (fused FFN: a down tile waits for
+// gate/up tiles that other blocks own), so it must not be larger than what is resident at once.
+// Asked once per device and kernel: blocks (or clusters of two) that fit, capped at one per SM
+// (pair of SMs). The answer assumes the GPU's shared memory is not held by other resident
+// kernels: a caller that runs another shared-memory-hungry kernel concurrently on the same GPU
+// must not overlap it with the fused launches.
+template <typename T, int SH>
+static int resident_units(int sms, int* out) {
+  static std::atomic<int> cached[MAX_DEVICES];
+  int dev = 0;
+  SY_CUDA(cudaGetDevice(&dev));
+  int units = cached[dev].load(std::memory_order_acquire);
+  if (!units) {
+    auto kern = gemm_umma_kernel<T, SH>;
+    SY_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
+    if (SH == SH_DUO) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(sms & ~1);
+      cfg.blockDim = dim3(GM_THREADS);
+      cfg.dynamicSmemBytes = GM_SMEM;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      SY_CUDA(cudaOccupancyMaxActiveClusters(&units, kern, &cfg));
+      if (units > sms / 2) units = sms / 2;
+    } else {
+      int per_sm = 0;
+      SY_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, GM_THREADS, GM_SMEM));
+      units = per_sm >= 1 ? sms : 0;
+    }
+    if (units < 1) return fail(SY_ERR_CUDA, "grouped kernel: no block of the tcgen05 kernel fits on this device");
+    cached[dev].store(units, std::memory_order_release);
+  }
+  *out = units;
+  return SY_OK;
+}
 
 template <typename T, int SH>
 static int launch_gemm(const GroupedArgs& a) {
@@ -975,50 +1142,28 @@ static int launch_gemm(const GroupedArgs& a) {
     k.p[i].a_rows = d.a_rows;
     k.p[i].scale = d.scale;
     k.p[i].C = d.C;
-    k.p[i].c_table = d.c_table;
+    k.p[i].use_table = d.use_table;
     k.p[i].Nout = d.n_out;
     k.p[i].K = d.k_dim;
     k.p[i].swiglu = d.swiglu;
   }
   k.begins = a.begins;
   k.ends = a.ends;
+  k.c_table = a.c_table;
   k.ranges = a.ranges;
   k.group_div = a.group_div;
   k.n_problems = a.n_problems;
   k.ready = a.ready;
+  k.wait_ns = wait_limit_ns();
+  k.ep = a.ep;
+  k.cmb = a.cmb;
+  int units = 0;
+  rc = resident_units<T, SH>(sms, &units);
+  if (rc != SY_OK) return rc;
   auto kern = gemm_umma_kernel<T, SH>;
-  // per device: 0 = not configured yet, else 1 + the number of CTA pairs that fit at once
-  static std::atomic<int> configured[MAX_DEVICES];
-  int dev = 0;
-  SY_CUDA(cudaGetDevice(&dev));
-  int state = configured[dev].load(std::memory_order_acquire);
-  if (!state) {
-    SY_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
-    int pairs = 0;
-    if (SH == SH_DUO) {
-      // The grid is persistent and its blocks wait on one another (fused FFN), so it must not be
-      // larger than what is resident at once: ask how many clusters of two fit.
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(sms & ~1);
-      cfg.blockDim = dim3(GM_THREADS);
-      cfg.dynamicSmemBytes = GM_SMEM;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      SY_CUDA(cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg));
-      if (pairs < 1) return fail(SY_ERR_CUDA, "grouped kernel: no cluster of two blocks fits on this device");
-      if (pairs > sms / 2) pairs = sms / 2;
-    }
-    state = 1 + pairs;
-    configured[dev].store(state, std::memory_order_release);
-  }
   if (SH == SH_DUO)
-    return launch_cluster_kernel(kern, 2, 2 * (state - 1), GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
-  return launch_kernel(kern, sms, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
+    return launch_cluster_kernel(kern, 2, 2 * units, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
+  return launch_kernel(kern, units, GM_THREADS, GM_SMEM, a.stream, "grouped tcgen05 launch", k);
 }
 
 // Which compute tile a batch gets. Measured on a B200 at OLMoE sizes, whole layer, Zipf-skewed
@@ -1026,15 +1171,23 @@ static int launch_gemm(const GroupedArgs& a) {
 // loses 1-6 % at 512 and 128, where more of its rows are padding; uniform routing moves the
 // crossover down, and the fused kernel alone gains up to 8 %. So: CTA pairs from 768 rows per
 // expert on average, for plain sorted batches (one range per expert, contiguous rows);
-// SY_GEMM_TILE=single|pair in the environment forces one. The two produce the same bits (the
-// same MMAs in the same k order).
+// SY_GEMM_TILE=single|pair in the environment (read once) forces one. The two produce the same
+// bits (the same MMAs in the same k order).
 constexpr int GM_DUO_MIN_MEAN_ROWS = 768;
+static std::atomic<int> g_forced_tile{-2};  // -2: not looked up yet; -1: automatic; else a shape
+static int forced_tile() {
+  int f = g_forced_tile.load(std::memory_order_relaxed);
+  if (f == -2) {
+    const char* v = getenv("SY_GEMM_TILE");
+    f = v && v[0] == 's' ? SH_PAIR : v && v[0] == 'p' ? SH_DUO : -1;
+    g_forced_tile.store(f, std::memory_order_relaxed);
+  }
+  return f;
+}
 static int compute_shape_for(const GroupedArgs& a, int rows) {
-  const char* v = getenv("SY_GEMM_TILE");
-  if (v && v[0] == 's') return SH_PAIR;
-  if (v && v[0] == 'p') return SH_DUO;
-  bool plain = a.group_div == 1;
-  for (int i = 0; i < a.n_problems; ++i) plain = plain && !a.p[i].a_rows && !a.p[i].c_table;
+  bool plain = a.group_div == 1 && !a.ep.arrive;
+  for (int i = 0; i < a.n_problems; ++i) plain = plain && !a.p[i].a_rows && !a.p[i].use_table;
+  if (plain && forced_tile() >= 0) return forced_tile();
   return plain && rows >= a.ranges * GM_DUO_MIN_MEAN_ROWS ? SH_DUO : SH_PAIR;
 }
 
@@ -1054,15 +1207,17 @@ int grouped_umma(bool pair, const char* name, const GroupedArgs& args, int rows)
     SY_REQUIRE(!(d.swiglu && d.scale), "%s: swiglu and scale are separate epilogues", name);
   }
   if (rows == 0) return SY_OK;
-  SY_REQUIRE(a.begins && a.ends, "%s: null pointer", name);
+  SY_REQUIRE(a.ep.arrive || (a.begins && a.ends), "%s: null pointer", name);
   for (int i = 0; i < a.n_problems; ++i) {
     const ProblemDesc& d = a.p[i];
-    SY_REQUIRE(d.A && d.B && (d.C || d.c_table), "%s: null pointer", name);
+    SY_REQUIRE(d.A && d.B && (d.C || d.use_table), "%s: null pointer", name);
+    SY_REQUIRE(!d.use_table || a.c_table || a.ep.arrive, "%s: no table of result rows", name);
     SY_REQUIRE(((uintptr_t)d.A % 16 == 0) && ((uintptr_t)d.B % 16 == 0) && ((uintptr_t)d.C % 16 == 0),
                "%s: A, B and C must be 16-byte aligned", name);
   }
   SY_REQUIRE(a.n_problems == 1 || a.ready, "%s: the fused form needs its scratch", name);
   const int shape = pair ? compute_shape_for(a, rows) : SH_STREAM;
+  SY_REQUIRE(!a.cmb.out || shape == SH_STREAM, "%s: the fused combine belongs to the streaming shape", name);
   if (a.dtype == SY_DTYPE_F16)
     return shape == SH_DUO    ? launch_gemm<__half, SH_DUO>(a)
            : shape == SH_PAIR ? launch_gemm<__half, SH_PAIR>(a)
@@ -1077,10 +1232,11 @@ static GroupedArgs single(const void* A, const int32_t* a_rows, const void* B, c
                           const void* scale, void* C, const unsigned long long* c_table, int dtype, void* stream) {
   GroupedArgs a;
   memset(&a, 0, sizeof(a));
-  a.p[0] = ProblemDesc{A, a_rows, B, n_out, k_dim, swiglu, scale, C, c_table};
+  a.p[0] = ProblemDesc{A, a_rows, B, n_out, k_dim, swiglu, scale, C, c_table != nullptr};
   a.n_problems = 1;
   a.begins = begins;
   a.ends = ends;
+  a.c_table = c_table;
   a.ranges = ranges;
   a.group_div = group_div;
   a.dtype = dtype;
@@ -1088,19 +1244,28 @@ static GroupedArgs single(const void* A, const int32_t* a_rows, const void* B, c
   return a;
 }
 
+// Both projections of the expert FFN as one launch's two problems.
+static GroupedArgs ffn_pair(const void* x, const int32_t* a_rows, const void* gate_up, const void* down, int hidden,
+                            int inter, const void* wsorted, void* act, void* y, int y_through_table, int32_t* scratch,
+                            int dtype, void* stream) {
+  GroupedArgs a;
+  memset(&a, 0, sizeof(a));
+  a.p[0] = ProblemDesc{x, a_rows, gate_up, inter, hidden, 1, nullptr, act, 0};
+  a.p[1] = ProblemDesc{act, nullptr, down, hidden, inter, 0, wsorted, y, y_through_table};
+  a.n_problems = 2;
+  a.ready = scratch;
+  a.dtype = dtype;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return a;
+}
+
 }  // namespace sy
 
-#ifdef SY_PROFILE
-extern "C" int sy_prof_read(unsigned long long* out, int reset) {
-  SY_CUDA(cudaDeviceSynchronize());
-  SY_CUDA(cudaMemcpyFromSymbol(out, sy::g_prof, sizeof(sy::g_prof)));
-  if (reset) {
-    unsigned long long zero[32] = {0};
-    SY_CUDA(cudaMemcpyToSymbol(sy::g_prof, zero, sizeof(zero)));
-  }
+extern "C" int sy_force_compute_tile(int tile) {
+  SY_REQUIRE(tile >= 0 && tile <= 2, "force_compute_tile: 0 = automatic, 1 = one CTA per tile, 2 = CTA pairs (got %d)", tile);
+  sy::g_forced_tile.store(tile == 0 ? -1 : tile == 1 ? sy::SH_PAIR : sy::SH_DUO, std::memory_order_relaxed);
   return SY_OK;
 }
-#endif
 
 extern "C" int sy_grouped_gemm(const void* A, const int32_t* a_rows, const void* B, const int32_t* offsets,
                                int n_experts, int rows, int n_out, int k_dim, int swiglu, const void* scale, void* C,
@@ -1138,18 +1303,68 @@ extern "C" int sy_expert_ffn(const void* x, const int32_t* a_rows, const void* g
                              const uint64_t* y_table, int32_t* scratch, int dtype, int compute_shape, void* stream) {
   using namespace sy;
   SY_REQUIRE(wsorted, "expert_ffn: null router weights");
-  GroupedArgs a;
-  memset(&a, 0, sizeof(a));
-  a.p[0] = ProblemDesc{x, a_rows, gate_up, inter, hidden, 1, nullptr, act, nullptr};
-  a.p[1] = ProblemDesc{act, nullptr, down, hidden, inter, 0, wsorted, y,
-                       reinterpret_cast<const unsigned long long*>(y_table)};
-  a.n_problems = 2;
+  GroupedArgs a = ffn_pair(x, a_rows, gate_up, down, hidden, inter, wsorted, act, y, y_table != nullptr, scratch, dtype,
+                           stream);
   a.begins = begins;
   a.ends = ends;
+  a.c_table = reinterpret_cast<const unsigned long long*>(y_table);
   a.ranges = n_ranges;
   a.group_div = ranges_per_expert;
-  a.ready = scratch;
-  a.dtype = dtype;
-  a.stream = static_cast<cudaStream_t>(stream);
   return grouped_umma(compute_shape != 0, "expert_ffn", a, rows_bound);
+}
+
+extern "C" size_t sy_expert_ffn_combine_scratch_bytes(int n_experts, int n_tokens, int hidden) {
+  return sizeof(int32_t) * ((size_t)(n_experts + 1) + (size_t)n_tokens * ((hidden + sy::GM_BM - 1) / sy::GM_BM));
+}
+
+extern "C" int sy_expert_ffn_combine(const void* x, const int32_t* token, const void* gate_up, const void* down,
+                                     const int32_t* offsets, int n_experts, int rows, int hidden, int inter,
+                                     const void* wsorted, void* act, void* y, const int32_t* pos_of, int top_k,
+                                     int n_tokens, void* out, int32_t* scratch, int dtype, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(wsorted && token && pos_of && out && offsets, "expert_ffn_combine: null pointer");
+  SY_REQUIRE(top_k >= 1 && top_k <= COMBINE_K && n_tokens >= 0 && rows == n_tokens * top_k,
+             "expert_ffn_combine: rows must be n_tokens * top_k with top_k <= %d (got %d, %d, %d)", COMBINE_K, rows,
+             n_tokens, top_k);
+  SY_REQUIRE((uintptr_t)out % 16 == 0, "expert_ffn_combine: out must be 16-byte aligned");
+  GroupedArgs a = ffn_pair(x, token, gate_up, down, hidden, inter, wsorted, act, y, 0, scratch, dtype, stream);
+  a.begins = offsets;
+  a.ends = offsets + 1;
+  a.ranges = n_experts;
+  a.group_div = 1;
+  a.cmb.out = out;
+  a.cmb.token = token;
+  a.cmb.pos_of = pos_of;
+  a.cmb.arrivals = scratch ? scratch + n_experts + 1 : nullptr;
+  a.cmb.k = top_k;
+  a.cmb.rows = rows;
+  return grouped_umma(false, "expert_ffn_combine", a, rows);
+}
+
+extern "C" int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const int32_t* meta, const int32_t* arrive_flags,
+                                const int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity,
+                                const void* gate_up, const void* down, int hidden, int inter, void* act,
+                                void* const* y_dst, int32_t* const* ret_flag_dst, int32_t* scratch, int dtype,
+                                int compute_shape, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= GM_MAX_RANKS && experts_per_rank >= 1 && capacity >= 1,
+             "ep_expert_ffn: 1..%d ranks (got %d)", GM_MAX_RANKS, n_ranks);
+  SY_REQUIRE(x_mail && w_mail && meta && arrive_flags && epoch_counter && y_dst && ret_flag_dst,
+             "ep_expert_ffn: null pointer");
+  GroupedArgs a = ffn_pair(x_mail, nullptr, gate_up, down, hidden, inter, w_mail, act, nullptr, 1, scratch, dtype, stream);
+  a.ranges = n_ranks * experts_per_rank;
+  a.group_div = n_ranks;
+  a.ep.arrive = arrive_flags;
+  a.ep.meta = meta;
+  a.ep.epoch_counter = epoch_counter;
+  a.ep.R = n_ranks;
+  a.ep.per = experts_per_rank;
+  a.ep.cap = capacity;
+  a.ep.out_row_bytes = hidden * 2;
+  for (int r = 0; r < n_ranks; ++r) {
+    a.ep.y[r] = static_cast<unsigned char*>(y_dst[r]);
+    a.ep.ret_flag[r] = ret_flag_dst[r];
+    SY_REQUIRE(a.ep.y[r] && a.ep.ret_flag[r] && (uintptr_t)a.ep.y[r] % 16 == 0, "ep_expert_ffn: bad target for rank %d", r);
+  }
+  return grouped_umma(compute_shape != 0, "ep_expert_ffn", a, n_ranks * capacity);
 }

@@ -1,10 +1,6 @@
 // route: router logits -> float32 softmax -> top-k experts and weights. One warp per token.
 //
-// Arithmetic contract (what makes the expert indices bit-exact against the reference kernel,
-// switchyard/csrc/moe_kernels.cu:23-71): expert e lives in lane e % 32, register e / 32; the
-// maximum and the sum of exp(v - max) are float32 xor-butterflies; selection runs on the exp
-// values, larger first and the LOWER expert index on equal values; weights are exp / sum,
-// divided by the sum of the picked weights when renormalising, rounded once to 16 bits.
+// The rule and its implementation are in route.cuh; replaces switchyard/csrc/moe_kernels.cu:23-89.
 #include "route.cuh"
 
 namespace sy {

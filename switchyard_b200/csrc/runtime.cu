@@ -36,6 +36,25 @@ bool pdl_enabled() {
   return on;
 }
 
+// How long a kernel of this library waits for a flag or barrier before it gives up and records
+// a status code. One value for all devices; SY_WAIT_LIMIT_MS in the environment sets the
+// initial value (read once), sy_set_wait_limit_ns replaces it at run time.
+static std::atomic<uint64_t> g_wait_limit_ns{0};
+
+uint64_t wait_limit_ns() {
+  uint64_t v = g_wait_limit_ns.load(std::memory_order_relaxed);
+  if (v == 0) {
+    v = 2000000000ull;
+    const char* e = getenv("SY_WAIT_LIMIT_MS");
+    if (e && e[0]) {
+      const long long ms = atoll(e);
+      if (ms > 0) v = (uint64_t)ms * 1000000ull;
+    }
+    g_wait_limit_ns.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
 int check_cuda(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return SY_OK;
   snprintf(t_error, sizeof(t_error), "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
@@ -65,7 +84,8 @@ static int device_info(DeviceInfo** out) {
       void* p = nullptr;
       SY_CUDA(cudaGetSymbolAddress(&p, g_status_word));
       d.status_word = static_cast<int*>(p);
-      SY_CUDA(cudaMemset(p, 0, sizeof(int)));
+      // (the word starts at zero: a __device__ variable without an initialiser is zero-filled
+      // when the module is loaded, so nothing has to be enqueued or synchronised here)
       d.ready.store(1, std::memory_order_release);
     }
   }
@@ -97,6 +117,27 @@ extern "C" const char* sy_last_error(void) { return sy::t_error; }
 
 extern "C" const char* sy_version(void) { return "switchyard_b200 0.1 (sm_100a)"; }
 
+extern "C" int sy_set_wait_limit_ns(uint64_t limit_ns) {
+  SY_REQUIRE(limit_ns >= 1000ull && limit_ns <= 60000000000ull, "set_wait_limit_ns: 1 us .. 60 s (got %llu ns)",
+             (unsigned long long)limit_ns);
+  sy::g_wait_limit_ns.store(limit_ns, std::memory_order_relaxed);
+  return SY_OK;
+}
+
+extern "C" uint64_t sy_wait_limit_ns(void) { return sy::wait_limit_ns(); }
+
+static const char* status_text(int v) {
+  switch (v) {
+    case sy::DS_TIMEOUT_FULL: return "a stage of the expert kernel's ring was never filled";
+    case sy::DS_TIMEOUT_EMPTY: return "a stage of the expert kernel's ring was never released";
+    case sy::DS_TIMEOUT_MMA: return "an accumulator was never committed";
+    case sy::DS_TIMEOUT_TMEM: return "an accumulator was never drained";
+    case sy::DS_TIMEOUT_FLAG: return "a flag (a peer's arrival or return signal, or an expert's readiness) never came";
+    case sy::DS_BAD_INDEX: return "an index outside its array was skipped";
+    default: return "unknown status";
+  }
+}
+
 extern "C" int sy_device_status(void* stream, int* status_out) {
   int* word = sy::device_status_word();
   if (!word) return SY_ERR_CUDA;
@@ -109,5 +150,6 @@ extern "C" int sy_device_status(void* stream, int* status_out) {
     SY_CUDA(cudaStreamSynchronize(s));
   }
   if (status_out) *status_out = v;
+  if (v != 0) return sy::fail(SY_ERR_DEVICE, "device status %d: %s", v, status_text(v));
   return SY_OK;
 }

@@ -14,6 +14,7 @@
 //
 // Replaces the reference's one-block-per-expert sort (switchyard/csrc/moe_kernels.cu:94-157),
 // which reads the whole list once per expert and calls torch for the prefix sum in between.
+#include <atomic>
 #include <mutex>
 
 #include "route.cuh"
@@ -48,7 +49,14 @@ static SortShape sort_shape(int m) {
   return s;
 }
 
+// idx[i], read through L2 when COHERENT (the entry may have been written by another block of
+// the same launch).
+template <bool COHERENT> __device__ __forceinline__ int load_choice(const int* idx, int i) {
+  return COHERENT ? __ldcg(idx + i) : idx[i];
+}
+
 // Per-warp expert counts of this block's chunk into wcount[warp][e] (shared, zeroed here).
+template <bool COHERENT = false>
 __device__ __forceinline__ void count_chunk(const int* idx, int m, int begin, int per_warp, int E,
                                             int* wcount) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,7 +66,7 @@ __device__ __forceinline__ void count_chunk(const int* idx, int m, int begin, in
   const int start = begin + warp * per_warp;
   for (int base = start; base < start + per_warp && base < m; base += 32) {
     int i = base + lane;
-    int e = i < m ? idx[i] : -1;
+    int e = i < m ? load_choice<COHERENT>(idx, i) : -1;
     bool ok = e >= 0 && e < E;
     unsigned group = __match_any_sync(0xffffffffu, ok ? e : -1);
     if (ok && lane == __ffs(group) - 1) mine[e] += __popc(group);
@@ -85,7 +93,7 @@ __device__ __forceinline__ void warp_scan_experts(const int* v, int E, int* out)
   if (lane == 0) out[E] = carry;
 }
 
-template <typename T>
+template <typename T, bool COHERENT = false>
 __device__ __forceinline__ void scatter_chunk(const int* idx, const T* w, int m, int k,
                                               int begin, int per_warp, int E, int* wbase,
                                               int* __restrict__ token, T* __restrict__ wsorted,
@@ -95,9 +103,12 @@ __device__ __forceinline__ void scatter_chunk(const int* idx, const T* w, int m,
   const int start = begin + warp * per_warp;
   for (int base = start; base < start + per_warp && base < m; base += 32) {
     int i = base + lane;
-    int e = i < m ? idx[i] : -1;
+    int e = i < m ? load_choice<COHERENT>(idx, i) : -1;
     bool ok = e >= 0 && e < E;
-    if (i < m && !ok) *status = DS_BAD_INDEX;  // an expert id outside [0, E): the row is skipped
+    if (i < m && !ok) {  // an expert id outside [0, E): the choice gets no row; combine skips it
+      *status = DS_BAD_INDEX;
+      pos_of[i] = -1;
+    }
     unsigned group = __match_any_sync(0xffffffffu, ok ? e : -1);
     int pos = 0;
     if (ok) pos = mine[e] + __popc(group & ((1u << lane) - 1u));
@@ -106,7 +117,7 @@ __device__ __forceinline__ void scatter_chunk(const int* idx, const T* w, int m,
     __syncwarp();
     if (ok) {
       token[pos] = i / k;
-      wsorted[pos] = w[i];
+      wsorted[pos] = COHERENT ? ldcg16(w + i) : w[i];
       pos_of[i] = pos;
     }
   }
@@ -190,6 +201,139 @@ route_sort_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int 
   }
   __syncthreads();
   scatter_chunk<T>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
+}
+
+// Decode-sized batches, everything before the experts in ONE launch: the router GEMM, the
+// routing and the sort. A block owns sixteen tokens. Its sixteen warps each take every
+// sixteenth 32-wide slice of the hidden dimension and multiply the sixteen token rows by all
+// E router rows over their slices with warp-level MMAs (the operands come straight from global
+// memory, 16 bytes per lane and row: a lane's eight consecutive k feed two MMAs, and because
+// both operands use the same assignment of k to fragment slots the products that are summed are
+// the right ones); the warps' partial sums meet in shared memory and are added in warp order, so
+// a token's logits depend on nothing but its own row. The sums are rounded to the 16-bit type
+// (what the router GEMM of the unfused path stores), an optional per-expert bias is added in
+// that type, every warp routes one token from shared memory, and the block that finishes last
+// (a ticket in `ticket`, which it leaves at zero) sorts all choices as sort_single_kernel does.
+// The logits are also written out when `logits_out` is given: the routing is the kernel rule of
+// route.cuh applied to exactly those values.
+// Replaces switchyard/kernels.py:30-32 (cuBLAS GEMM, then route) and moe_kernels.cu:142-157.
+constexpr int RF_TOKENS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(SORT_THREADS)
+route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const T* __restrict__ bias, int n_tokens, int E,
+                   int K, int k, int norm, int per_block, T* __restrict__ logits_out, int* idx, T* w, int* __restrict__ counts,
+                   int* __restrict__ offsets, int* __restrict__ token, T* __restrict__ wsorted, int* __restrict__ pos_of,
+                   int* ticket, int* status) {
+  extern __shared__ int sh[];
+  float* partial = reinterpret_cast<float*>(sh);  // [SORT_WARPS][RF_TOKENS][E]
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int t0 = blockIdx.x * RF_TOKENS;
+  const int n_tiles = E >> 3;  // eight experts per MMA
+  pdl_launch_dependents();
+  pdl_wait();  // the hidden states come from the caller's previous kernel
+
+  // ---- router GEMM: this warp's slices of k
+  float acc[ROUTE_MAX_E / 8][4];
+#pragma unroll
+  for (int n = 0; n < ROUTE_MAX_E / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  const bool row_a = t0 + g < n_tokens, row_b = t0 + g + 8 < n_tokens;
+  const uint4* ha = reinterpret_cast<const uint4*>(h + (size_t)(t0 + g) * K) + q;
+  const uint4* hb = reinterpret_cast<const uint4*>(h + (size_t)(t0 + g + 8) * K) + q;
+  const uint4* rw = reinterpret_cast<const uint4*>(router + (size_t)g * K) + q;
+  const size_t tile_stride = (size_t)K;  // uint4 units between expert n and expert n + 8: 8 rows * K / 8
+  for (int c = warp; c * 32 < K; c += SORT_WARPS) {
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 a = row_a ? __ldg(ha + c * 4) : zero, b = row_b ? __ldg(hb + c * 4) : zero;
+#pragma unroll
+    for (int n = 0; n < ROUTE_MAX_E / 8; ++n) {
+      if (n < n_tiles) {
+        const uint4 r = __ldg(rw + n * tile_stride + c * 4);
+        mma_16816<T>(acc[n], a.x, b.x, a.y, b.y, r.x, r.y);
+        mma_16816<T>(acc[n], a.z, b.z, a.w, b.w, r.z, r.w);
+      }
+    }
+  }
+  float* mine = partial + (size_t)warp * RF_TOKENS * E;
+#pragma unroll
+  for (int n = 0; n < ROUTE_MAX_E / 8; ++n) {
+    if (n < n_tiles) {
+      const int col = n * 8 + q * 2;
+      mine[g * E + col] = acc[n][0];
+      mine[g * E + col + 1] = acc[n][1];
+      mine[(g + 8) * E + col] = acc[n][2];
+      mine[(g + 8) * E + col + 1] = acc[n][3];
+    }
+  }
+  __syncthreads();
+  // ---- the warps' partial sums, added in warp order; rounded; bias; kept as float in partial[0]
+  float sums[(RF_TOKENS * ROUTE_MAX_E) / SORT_THREADS];
+#pragma unroll
+  for (int j = 0; j < (RF_TOKENS * ROUTE_MAX_E) / SORT_THREADS; ++j) {
+    const int i = threadIdx.x + j * SORT_THREADS;
+    float s = 0.f;
+    if (i < RF_TOKENS * E)
+      for (int wi = 0; wi < SORT_WARPS; ++wi) s += partial[(size_t)wi * RF_TOKENS * E + i];
+    sums[j] = s;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < (RF_TOKENS * ROUTE_MAX_E) / SORT_THREADS; ++j) {
+    const int i = threadIdx.x + j * SORT_THREADS;
+    if (i < RF_TOKENS * E) {
+      T v = Elem<T>::from_f(sums[j]);
+      if (bias) v = Elem<T>::from_f(Elem<T>::to_f(v) + Elem<T>::to_f(bias[i % E]));
+      partial[i] = Elem<T>::to_f(v);
+      const int t = t0 + i / E;
+      if (logits_out && t < n_tokens) logits_out[(size_t)t * E + i % E] = v;
+    }
+  }
+  __syncthreads();
+  // ---- routing: a warp per token
+  if (t0 + warp < n_tokens)
+    route_token_any<T>(partial + warp * E, E, k, norm, lane, idx + (size_t)(t0 + warp) * k, w + (size_t)(t0 + warp) * k);
+  // ---- the last block to get here sorts every block's choices
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int last = 1;
+    if (gridDim.x > 1) {
+      __threadfence();
+      last = atomicAdd(ticket, 1) == (int)gridDim.x - 1;
+      if (last) *ticket = 0;
+      __threadfence();
+    }
+    s_last = last;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  int* wcount = sh;                       // [SORT_WARPS][E]; the partial sums are no longer needed
+  int* total = wcount + SORT_WARPS * E;   // [E]
+  int* off = total + E;                   // [E + 1]
+  const int per_warp = per_block / SORT_WARPS;
+  const int m = n_tokens * k;
+  count_chunk<true>(idx, m, 0, per_warp, E, wcount);
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int s = 0;
+    for (int wi = 0; wi < SORT_WARPS; ++wi) s += wcount[wi * E + e];
+    total[e] = s;
+    counts[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) warp_scan_experts(total, E, off);
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
+    int at = off[e];
+    for (int wi = 0; wi < SORT_WARPS; ++wi) {
+      int c = wcount[wi * E + e];
+      wcount[wi * E + e] = at;
+      at += c;
+    }
+  }
+  __syncthreads();
+  scatter_chunk<T, true>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
 }
 
 // Launch 1 of the multi-block sort: this block's expert counts into table[block][e].
@@ -328,6 +472,58 @@ extern "C" int sy_route_sort(const void* logits, int n_tokens, int n_experts, in
                        static_cast<const __nv_bfloat16*>(logits), n_tokens, n_experts, top_k, norm_topk_prob,
                        sh.per_block, idx, static_cast<__nv_bfloat16*>(w), counts, offsets, token,
                        static_cast<__nv_bfloat16*>(wsorted), pos_of, status);
+}
+
+extern "C" int sy_route_fused_max_tokens(void) { return sy::SORT_SINGLE_MAX / 8; }
+
+extern "C" int sy_route_fused(const void* h, const void* router, const void* bias, int n_tokens, int n_experts, int hidden,
+                              int top_k, int norm_topk_prob, int dtype, void* logits_out, int32_t* idx, void* w,
+                              int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                              int32_t* ticket, void* stream) {
+  using namespace sy;
+  SY_REQUIRE(n_tokens >= 1 && n_experts >= 8 && n_experts <= ROUTE_MAX_E && n_experts % 8 == 0 && top_k >= 1 &&
+                 top_k <= 8 && top_k <= n_experts,
+             "route_fused: 8..128 experts in multiples of 8, top-8, at least one token (got N=%d, E=%d, k=%d)", n_tokens,
+             n_experts, top_k);
+  SY_REQUIRE((long long)n_tokens * top_k <= SORT_SINGLE_MAX, "route_fused: at most %d choices (got %lld)",
+             SORT_SINGLE_MAX, (long long)n_tokens * top_k);
+  SY_REQUIRE(hidden >= 32 && hidden % 32 == 0, "route_fused: hidden must be a multiple of 32 (got %d)", hidden);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "route_fused: dtype must be f16 or bf16");
+  SY_REQUIRE(h && router && idx && w && counts && offsets && token && wsorted && pos_of && ticket,
+             "route_fused: null pointer");
+  SY_REQUIRE(((uintptr_t)h % 16 == 0) && ((uintptr_t)router % 16 == 0), "route_fused: h and router must be 16-byte aligned");
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  const int m = n_tokens * top_k;
+  const SortShape sh = sort_shape(m);
+  const size_t sort_smem = (size_t)(SORT_WARPS * n_experts + 3 * n_experts + 1) * sizeof(int);
+  const size_t gemm_smem = (size_t)SORT_WARPS * RF_TOKENS * n_experts * sizeof(float);
+  const size_t smem = sort_smem > gemm_smem ? sort_smem : gemm_smem;
+  const int blocks = (n_tokens + RF_TOKENS - 1) / RF_TOKENS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  static std::atomic<int> configured[MAX_DEVICES][2];
+  int dev = 0;
+  SY_CUDA(cudaGetDevice(&dev));
+  const int which = dtype == SY_DTYPE_F16 ? 0 : 1;
+  if (!configured[dev][which].load(std::memory_order_acquire)) {
+    const size_t most = (size_t)SORT_WARPS * RF_TOKENS * ROUTE_MAX_E * sizeof(float);
+    if (which == 0)
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+    else
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+    configured[dev][which].store(1, std::memory_order_release);
+  }
+  if (dtype == SY_DTYPE_F16)
+    return launch_kernel(route_fused_kernel<__half>, blocks, SORT_THREADS, smem, s, "route_fused launch",
+                         static_cast<const __half*>(h), static_cast<const __half*>(router),
+                         static_cast<const __half*>(bias), n_tokens, n_experts, hidden, top_k, norm_topk_prob,
+                         sh.per_block, static_cast<__half*>(logits_out), idx, static_cast<__half*>(w), counts, offsets,
+                         token, static_cast<__half*>(wsorted), pos_of, ticket, status);
+  return launch_kernel(route_fused_kernel<__nv_bfloat16>, blocks, SORT_THREADS, smem, s, "route_fused launch",
+                       static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(router),
+                       static_cast<const __nv_bfloat16*>(bias), n_tokens, n_experts, hidden, top_k, norm_topk_prob,
+                       sh.per_block, static_cast<__nv_bfloat16*>(logits_out), idx, static_cast<__nv_bfloat16*>(w), counts,
+                       offsets, token, static_cast<__nv_bfloat16*>(wsorted), pos_of, ticket, status);
 }
 
 // ---- sort_by_expert_static: the same sort for callers that cannot hand over scratch ----------

@@ -14,7 +14,12 @@ Differences a caller can observe:
     from `offsets`, so the "gemm" mode never reads anything back to the host;
   * there is no cuBLAS mode; "cublas" is accepted as an alias of "gemm";
   * `experts(mode="auto")` chooses from the token count, not from a device-to-host read of
-    the largest expert's row count, so the layer never synchronises.
+    the largest expert's row count, so the layer never synchronises;
+  * `moe_layer` with at most ROUTE_FUSED_MAX_TOKENS tokens computes the router logits inside the
+    routing launch (`route_fused`) instead of calling the library GEMM: the logits are the same
+    dot products summed in another order, so they can differ from `F.linear`'s in the last bit
+    and a token whose k-th and (k+1)-th logits are that close may pick the other expert.
+    `route(h, router, ...)` keeps the library GEMM, as in the reference.
 """
 
 import ctypes
@@ -67,25 +72,40 @@ class _Device:
         return False
 
 
+class Scratch:
+    """Zeroed int32 device memory that the fused launches count in (per-expert readiness, the
+    fused combine's arrivals, the fused routing's ticket). Every launch leaves it zero, so it is
+    allocated once and grown on demand. Launches that share one Scratch must not overlap on the
+    GPU: eager calls use one per (device, stream); an object that replays its launches from a
+    CUDA graph on whatever stream is current (GraphedLayer) owns its own."""
+
+    def __init__(self, device):
+        self.device = device
+        self.main = torch.zeros(1024, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ints(self, n):
+        if self.main.numel() < n:
+            self.main = torch.zeros(max(n, 2 * self.main.numel()), dtype=torch.int32, device=self.device)
+        return self.main
+
+
 class Ext:
     """The eight operations of the reference's extension module
-    (switchyard/csrc/moe_kernels.cu:491-500), on torch tensors."""
+    (switchyard/csrc/moe_kernels.cu:491-500), on torch tensors, plus this library's fused ones."""
 
     def __init__(self):
         self.lib = _lib.load()
-        self._ffn_scratch = {}  # (device, stream) -> zeroed counters of the fused FFN kernel
+        self._scratch = {}  # (device index, stream handle) -> Scratch of eager calls
 
-    def ffn_scratch(self, device, stream, experts):
-        """The fused FFN kernel's per-expert counters: zero-initialised once, left zero by every
-        launch, and private to one stream (launches sharing them must not overlap)."""
-        key = (device.index, stream, experts)
-        t = self._ffn_scratch.get(key)
-        if t is None:
-            t = torch.zeros(experts + 1, dtype=torch.int32, device=device)
-            self._ffn_scratch[key] = t
-        return t
+    def scratch(self, device, stream):
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        s = self._scratch.get((index, stream))
+        if s is None:
+            s = self._scratch[(index, stream)] = Scratch(torch.device("cuda", index))
+        return s
 
-    def expert_ffn(self, x, a_rows, gate_up, down, offsets, rows, wsorted, compute_shape):
+    def expert_ffn(self, x, a_rows, gate_up, down, offsets, rows, wsorted, compute_shape, scratch=None):
         """Both projections of the expert FFN in one launch (sy_expert_ffn): returns y [rows, H]."""
         _check(x, "x"), _check(gate_up, "gate_up"), _check(down, "down"), _check(offsets, "offsets")
         _check(wsorted, "wsorted")
@@ -102,12 +122,70 @@ class Ext:
             return y
         act = torch.empty(rows, I2 // 2, dtype=x.dtype, device=x.device)
         with _Device(x.device) as stream:
-            scratch = self.ffn_scratch(x.device, stream, E)
+            ints = (scratch or self.scratch(x.device, stream)).ints(E + 1)
             _lib.check(self.lib.sy_expert_ffn(_ptr(x), _ptr(a_rows), _ptr(gate_up), _ptr(down), _ptr(offsets),
                                               offsets.data_ptr() + 4, E, 1, int(rows), H, I2 // 2, _ptr(wsorted),
-                                              _ptr(act), _ptr(y), None, _ptr(scratch), code, int(compute_shape), stream),
+                                              _ptr(act), _ptr(y), None, _ptr(ints), code, int(compute_shape), stream),
                        "expert_ffn")
         return y
+
+    def expert_ffn_combine(self, x, token, gate_up, down, offsets, wsorted, pos_of, top_k, scratch=None):
+        """The expert FFN in its streaming shape with the combine folded into the down projection's
+        epilogue (sy_expert_ffn_combine): one launch from sorted rows to the layer's output.
+        Returns out [N, H], bit-identical to expert_ffn followed by combine."""
+        for t, name in ((x, "x"), (token, "token"), (gate_up, "gate_up"), (down, "down"), (offsets, "offsets"),
+                        (wsorted, "wsorted"), (pos_of, "pos_of")):
+            _check(t, name)
+        code = _dtype_code(x, "expert_ffn_combine")
+        E, I2, H = gate_up.shape
+        N, rows = x.shape[0], token.numel()
+        if down.shape != (E, H, I2 // 2) or x.shape[1] != H or gate_up.dtype != x.dtype or down.dtype != x.dtype:
+            raise RuntimeError("expert_ffn_combine: shapes or dtypes do not match")
+        if rows != N * top_k or pos_of.numel() != rows or offsets.numel() != E + 1:
+            raise RuntimeError("expert_ffn_combine: rows must be tokens * top_k")
+        out = torch.empty(N, H, dtype=x.dtype, device=x.device)
+        if rows == 0:
+            return out
+        both = torch.empty(rows, I2 // 2 + H, dtype=x.dtype, device=x.device)  # act | y: one allocation
+        act, y = both.view(-1)[:rows * (I2 // 2)], both.view(-1)[rows * (I2 // 2):]
+        need = self.lib.sy_expert_ffn_combine_scratch_bytes(E, N, H) // 4
+        with _Device(x.device) as stream:
+            ints = (scratch or self.scratch(x.device, stream)).ints(need)
+            _lib.check(self.lib.sy_expert_ffn_combine(_ptr(x), _ptr(token), _ptr(gate_up), _ptr(down), _ptr(offsets), E,
+                                                      rows, H, I2 // 2, _ptr(wsorted), _ptr(act), _ptr(y), _ptr(pos_of),
+                                                      int(top_k), N, _ptr(out), _ptr(ints), code, stream),
+                       "expert_ffn_combine")
+        return out
+
+    def route_fused(self, h, router, k, norm, bias=None, logits=False, scratch=None):
+        """Router GEMM + route + sort_by_expert in one launch (sy_route_fused), for decode-sized
+        batches: returns [idx, w, counts, offsets, token, wsorted, pos_of] (+ the logits the routing
+        was made from when logits=True)."""
+        _check(h, "h"), _check(router, "router")
+        code = _dtype_code(h, "route_fused")
+        N, H = h.shape
+        E = router.shape[0]
+        if router.dtype != h.dtype or router.shape[1] != H:
+            raise RuntimeError("route_fused: h and router do not match")
+        if bias is not None:
+            _check(bias, "bias")
+            if bias.dtype != h.dtype or bias.numel() != E:
+                raise RuntimeError("route_fused: bias must be [E] in h's dtype")
+        dev, M = h.device, N * k
+        ints = torch.empty(2 * E + 1 + 3 * M, dtype=torch.int32, device=dev)
+        counts, offsets = ints[:E], ints[E:2 * E + 1]
+        token, pos_of = ints[2 * E + 1:2 * E + 1 + M], ints[2 * E + 1 + M:2 * E + 1 + 2 * M]
+        idx = ints[2 * E + 1 + 2 * M:].view(N, k)
+        halves = torch.empty(2 * M, dtype=h.dtype, device=dev)
+        w, wsorted = halves[:M].view(N, k), halves[M:]
+        dump = torch.empty(N, E, dtype=h.dtype, device=dev) if logits else None
+        with _Device(dev) as stream:
+            ticket = (scratch or self.scratch(dev, stream)).ticket
+            _lib.check(self.lib.sy_route_fused(_ptr(h), _ptr(router), _ptr(bias), N, E, H, int(k), int(bool(norm)), code,
+                                               _ptr(dump), _ptr(idx), _ptr(w), _ptr(counts), _ptr(offsets), _ptr(token),
+                                               _ptr(wsorted), _ptr(pos_of), _ptr(ticket), stream), "route_fused")
+        res = [idx, w, counts, offsets, token, wsorted, pos_of]
+        return res + [dump] if logits else res
 
     def route(self, logits, k, norm):
         _check(logits, "logits")
@@ -229,12 +307,26 @@ class Ext:
 
     def device_status(self, device=None):
         """Waits for the current stream and returns (and clears) the device's kernel status
-        word: 0 unless a kernel gave up on a bounded wait. For tests and error paths."""
+        word: 0 unless a kernel gave up on a bounded wait or skipped a bad index."""
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         v = ctypes.c_int(0)
         with _Device(dev) as stream:
-            _lib.check(self.lib.sy_device_status(stream, ctypes.byref(v)), "device_status")
+            rc = self.lib.sy_device_status(stream, ctypes.byref(v))
+            if rc != _lib.SY_ERR_DEVICE:
+                _lib.check(rc, "device_status")
         return v.value
+
+    def check_device(self, device=None):
+        """Raises RuntimeError if a kernel on `device` gave up on a bounded wait since the last
+        check (its results are then garbage). Waits for the current stream; call it at the end of
+        a request or a decode step, not per layer."""
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        with _Device(dev) as stream:
+            _lib.check(self.lib.sy_device_status(stream, None), "device_status")
+
+    def set_wait_limit(self, seconds):
+        """How long kernels wait for a flag or for one another before giving up (default 2 s)."""
+        _lib.check(self.lib.sy_set_wait_limit_ns(int(seconds * 1e9)), "set_wait_limit_ns")
 
 
 def ext():
@@ -281,7 +373,7 @@ def pick(max_rows):
     return "gemv" if max_rows <= GEMV_MAX_ROWS else "gemm"
 
 
-def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_counts=None):
+def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_counts=None, scratch=None):
     """The experts over rows already sorted by expert: row i is x[a_rows[i]] (or x[i] when
     a_rows is None); expert e owns rows offsets[e]:offsets[e+1]. Returns each row's expert
     output scaled by its router weight, [rows, H] (switchyard/kernels.py:48-73). `counts` and
@@ -293,7 +385,7 @@ def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_cou
     # one launch for both projections (bit-identical to grouped_gemv / grouped_gemm called twice,
     # which remain available on ext() as in the reference)
     if mode == "gemv":
-        return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 0)
+        return E.expert_ffn(x, a_rows, gate_up, down, offsets, rows, wsorted, 0, scratch)
     if mode in ("gemm", "cublas"):
         # Compute-bound batches: bring the rows into expert order first (one streaming copy),
         # so that both projections load their token tiles as contiguous TMA boxes. Gathering
@@ -303,44 +395,75 @@ def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_cou
             xs = torch.empty(rows, x.shape[1], dtype=x.dtype, device=x.device)
             E.gather_rows(x, a_rows, xs)
             x = xs
-        return E.expert_ffn(x, None, gate_up, down, offsets, rows, wsorted, 1)
+        return E.expert_ffn(x, None, gate_up, down, offsets, rows, wsorted, 1, scratch)
     raise RuntimeError(f"ffn: unknown mode {mode!r}")
+
+
+def _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch=None):
+    """From sorted choices (idx, w, counts, offsets, token, wsorted, pos_of) to the layer's output."""
+    idx, _, counts, offsets, token, wsorted, pos_of = srt
+    if mode == "auto":
+        mode = auto_mode(idx.numel(), gate_up.shape[0])  # no device-to-host read
+    if mode == "gemv" and 0 < top_k <= 8 and h.shape[0] > 0:
+        # streaming shape: the combine rides in the down projection's epilogue (one launch)
+        return ext().expert_ffn_combine(h.contiguous(), token, gate_up, down, offsets, wsorted, pos_of, top_k, scratch)
+    y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode, scratch=scratch)
+    return ext().combine(y, pos_of, idx, h.shape[0])
 
 
 def experts(h, idx, w, gate_up, down, mode="auto"):
     """The experts of one MoE layer on this GPU for routing (idx, w) computed already: sort by
     expert, SwiGLU projection reading rows of h in place, down projection scaled by the router
     weights, combine (switchyard/kernels.py:76-88). idx int32 [N,k] of local expert ids."""
-    E = ext()
-    N = h.shape[0]
     idx = idx.contiguous()
-    counts, offsets, token, wsorted, pos_of = E.sort_by_expert(idx, w.contiguous(), gate_up.shape[0])
-    if mode == "auto":
-        mode = auto_mode(idx.numel(), gate_up.shape[0])  # no device-to-host read
-    y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode)
-    return E.combine(y, pos_of, idx, N)
+    w = w.contiguous()
+    srt = ext().sort_by_expert(idx, w, gate_up.shape[0])
+    return _sorted_experts(h, [idx, w] + srt, gate_up, down, idx.shape[1], mode)
 
 
 ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what one block can route and sort
 # Measured on a B200: the one-block route+sort wins while every warp of the block routes at most
 # one token; beyond that the separate routing kernel (a warp per token, many blocks) is faster.
 ROUTE_SORT_MAX_TOKENS = 16
+# Up to this many tokens the router GEMM, the routing and the sort are ONE launch (route_fused).
+ROUTE_FUSED_MAX_TOKENS = 64
 
 
-def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
-    """route + experts (switchyard/kernels.py:91-93). Decode-sized batches take the fused
-    route+sort launch; the results are bit-identical to route() followed by experts()."""
-    N, E = h.shape[0], gate_up.shape[0]
-    if 0 < N <= ROUTE_SORT_MAX_TOKENS and N * top_k <= ROUTE_SORT_MAX_CHOICES and router.shape[0] <= 128:
-        X = ext()
-        idx, w, counts, offsets, token, wsorted, pos_of = X.route_sort(F.linear(h, router).contiguous(), top_k,
-                                                                        norm_topk_prob)
-        if mode == "auto":
-            mode = auto_mode(N * top_k, E)
-        y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode)
-        return X.combine(y, pos_of, idx, N)
-    idx, w = route(h, router, top_k, norm_topk_prob)
-    return experts(h, idx, w, gate_up, down, mode)
+def fused_routing_applies(n_tokens, n_experts, hidden, top_k):
+    return (0 < n_tokens <= ROUTE_FUSED_MAX_TOKENS and n_tokens * top_k <= ROUTE_SORT_MAX_CHOICES and
+            8 <= n_experts <= 128 and n_experts % 8 == 0 and hidden % 32 == 0 and 1 <= top_k <= 8)
+
+
+def route_and_sort(h, router, top_k, norm_topk_prob, bias=None, scratch=None):
+    """Everything before the experts: [idx, w, counts, offsets, token, wsorted, pos_of] for h's
+    tokens. One launch for decode-sized batches (router GEMM included), the library GEMM followed
+    by route (+ sort) otherwise. bias: optional [E] tensor in h's dtype added to the logits."""
+    X = ext()
+    N, E = h.shape[0], router.shape[0]
+    if fused_routing_applies(N, E, h.shape[1], top_k):
+        return X.route_fused(h.contiguous(), router, top_k, norm_topk_prob, bias, scratch=scratch)
+    logits = F.linear(h, router)
+    if bias is not None:
+        logits = logits + bias
+    logits = logits.contiguous()
+    if 0 < N <= ROUTE_SORT_MAX_TOKENS and N * top_k <= ROUTE_SORT_MAX_CHOICES and E <= 128:
+        return X.route_sort(logits, top_k, norm_topk_prob)
+    idx, w = X.route(logits, top_k, norm_topk_prob)
+    return [idx, w] + X.sort_by_expert(idx, w, E)
+
+
+def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto", scratch=None):
+    """route + experts (switchyard/kernels.py:91-93). Decode-sized batches in the streaming mode
+    are two launches: route_fused, then the expert FFN with the combine in its epilogue."""
+    srt = route_and_sort(h, router, top_k, norm_topk_prob, scratch=scratch)
+    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
+
+
+def moe_layer_with_bias(h, router, gate_up, down, top_k, norm_topk_prob, mode, bias, scratch=None):
+    """moe_layer with a per-expert bias [E] (h's dtype) added to the router logits before routing:
+    how the benchmarks apply their synthetic routing skew."""
+    srt = route_and_sort(h, router, top_k, norm_topk_prob, bias, scratch)
+    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
 
 
 class GraphedLayer:
@@ -349,12 +472,14 @@ class GraphedLayer:
     captures its decode step the same way). Call it with h [N,H], on the device or in pinned
     host memory; the result is a buffer owned by this object (valid until the next call with
     the same N), or is copied into `out` (device or pinned host memory) when given. Everything is
-    enqueued on the current stream; nothing synchronises."""
+    enqueued on the current stream; nothing synchronises. `check()` raises if one of the replayed
+    kernels gave up on a bounded wait (call it when a request or a decode step ends)."""
 
     def __init__(self, router, gate_up, down, top_k, norm_topk_prob, mode="auto"):
         self.args = (router, gate_up, down, top_k, norm_topk_prob, mode)
         self.device = gate_up.device
         self.graphs = {}  # N -> (graph, static input, static output)
+        self.scratch = Scratch(self.device)  # the captured launches' counters: not shared with anyone
 
     def _capture(self, N, dtype):
         router, gate_up, down, top_k, norm, mode = self.args
@@ -362,12 +487,12 @@ class GraphedLayer:
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            for _ in range(2):  # first use loads the library, cuBLAS picks its kernel
-                moe_layer(x, router, gate_up, down, top_k, norm, mode)
+            for _ in range(2):  # first use loads the library, cuBLAS picks its kernel, the scratch grows
+                moe_layer(x, router, gate_up, down, top_k, norm, mode, self.scratch)
             side.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
-                y = moe_layer(x, router, gate_up, down, top_k, norm, mode)
+                y = moe_layer(x, router, gate_up, down, top_k, norm, mode, self.scratch)
         torch.cuda.current_stream(self.device).wait_stream(side)
         self.graphs[N] = (g, x, y)
         return self.graphs[N]
@@ -381,3 +506,6 @@ class GraphedLayer:
             return y
         out.copy_(y, non_blocking=True)
         return out
+
+    def check(self):
+        ext().check_device(self.device)

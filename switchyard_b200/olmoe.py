@@ -7,10 +7,13 @@ present. This module is the same caller written for the one-process-per-GPU runt
 reference checkout exists: attention is data-parallel (every rank serves its own requests with
 its own KV cache), the experts of every layer are split over the ranks.
 
-It follows the reference model's structure and numerics (switchyard/model.py:14-162): RMSNorm
-in float32, QK-norm, rotate-half RoPE, left-padded batches, greedy decoding, and an MoE hook
-`moe(layer, h) -> [B*T, H]` between attention and the residual add (its `self.moe(i, h)`). Attention itself is off the measured path and uses
-torch.nn.functional.scaled_dot_product_attention.
+It computes what the reference's model computes (switchyard/model.py:14-162: OLMoE with
+float32 RMSNorm, QK-norm, rotary embeddings on half-split heads, left-padded batches, greedy
+decoding) and has the same MoE hook `moe(layer, h) -> [B*T, H]` between attention and the
+residual add (its `self.moe(i, h)`), but is laid out for a decode loop on one large GPU: the
+three input projections of a layer are one GEMM over a fused weight, rotary factors come from a
+table built once, the KV cache of all layers is one allocation, and attention itself (off the
+measured path) is torch.nn.functional.scaled_dot_product_attention.
 
 A decode step has fixed shapes (one new token per request, attention over the whole cache with
 a validity mask, positions kept on the device), so `DecodeGraph` captures it - all layers,
@@ -101,26 +104,44 @@ def from_hf_state_dict(sd, c, dtype=torch.float32, device="cpu"):
     return w
 
 
-def rmsnorm(x, w, eps):
-    xf = x.float()
-    return w * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+def scaled_norm(x, weight, eps):
+    """RMS normalisation computed in float32, result in x's dtype, times the learned scale."""
+    return weight * F.rms_norm(x.float(), (x.shape[-1],), eps=eps).to(x.dtype)
 
 
-def rotate_half(x):
-    a, b = x.chunk(2, dim=-1)
-    return torch.cat([-b, a], dim=-1)
+class RotaryTable:
+    """cos / sin of every position below `max_positions` for one head, in the model's dtype
+    (the angles are computed in float32 and rounded once). Only the first half of a head's
+    dimensions is stored: dimension j and j + head_dim/2 share an angle."""
+
+    def __init__(self, head_dim, theta, max_positions, dtype, device):
+        half = torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim
+        angles = torch.arange(max_positions, dtype=torch.float32, device=device)[:, None] * (1.0 / theta ** half)[None]
+        self.cos, self.sin = angles.cos().to(dtype), angles.sin().to(dtype)
+
+    def at(self, positions):
+        """positions [B, T] -> (cos, sin), each [B, 1, T, head_dim/2] (broadcast over heads)."""
+        flat = positions.reshape(-1)
+        shape = (*positions.shape, -1)
+        return self.cos[flat].view(shape)[:, None], self.sin[flat].view(shape)[:, None]
+
+
+def rotate(x, cos, sin):
+    """Rotary embedding of x [B, heads, T, head_dim]: the pair (x[j], x[j + head_dim/2]) is
+    turned by its position's angle."""
+    lo, hi = x.chunk(2, dim=-1)
+    return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin], dim=-1)
 
 
 class Cache:
-    """Keys and values of every layer, [B, kv_heads, capacity, head_dim]; `valid` marks real
-    tokens (batches are left-padded); `next_pos` is each request's next rotary position and
-    `length` the number of cache slots in use, both on the device so that a decode step can be
-    replayed from a CUDA graph."""
+    """Keys and values of all layers in one allocation, [layers, 2, B, kv_heads, capacity,
+    head_dim] (`k[i]`, `v[i]` are views); `valid` marks real tokens (batches are left-padded);
+    `next_pos` is each request's next rotary position and `length` the number of cache slots in
+    use, both on the device so that a decode step can be replayed from a CUDA graph."""
 
     def __init__(self, c, batch, capacity, dtype, device):
-        shape = (batch, c.kv_heads, capacity, c.head_dim)
-        self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(c.layers)]
-        self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(c.layers)]
+        self.store = torch.zeros(c.layers, 2, batch, c.kv_heads, capacity, c.head_dim, dtype=dtype, device=device)
+        self.k, self.v = list(self.store[:, 0]), list(self.store[:, 1])
         self.valid = torch.zeros(batch, capacity, dtype=torch.bool, device=device)
         self.next_pos = torch.zeros(batch, dtype=torch.int64, device=device)
         self.length = torch.zeros((), dtype=torch.int64, device=device)
@@ -132,35 +153,29 @@ class Decoder:
 
     def __init__(self, config, weights, moe):
         self.c, self.w, self.moe = config, weights, moe
-        dev = weights["embed"].device
-        self.inv_freq = 1.0 / (config.rope_theta ** (torch.arange(0, config.head_dim, 2, dtype=torch.int64, device=dev)
-                                                      .float() / config.head_dim))
+        c = config
+        embed = weights["embed"]
+        self.rope = RotaryTable(c.head_dim, c.rope_theta, c.max_positions, embed.dtype, embed.device)
+        # one GEMM for the three input projections of a layer, one norm for q and k
+        self.wqkv = [torch.cat([L["wq"], L["wk"], L["wv"]]) for L in weights["layers"]]
+        self.qd, self.kd = c.heads * c.head_dim, c.kv_heads * c.head_dim
 
-    def _rope(self, positions, dtype):
-        freqs = positions[..., None].float() * self.inv_freq
-        emb = torch.cat([freqs, freqs], dim=-1)
-        return emb.cos().to(dtype)[:, None], emb.sin().to(dtype)[:, None]
-
-    def _qkv(self, L, x, cos, sin):
-        c = self.c
+    def _qkv(self, i, x, cos, sin):
+        """Normed, rotated queries and keys and the values of layer i for x [B, T, H], each
+        [B, heads, T, head_dim]."""
+        c, L = self.c, self.w["layers"][i]
         B, T, _ = x.shape
-        q = rmsnorm(F.linear(x, L["wq"]), L["q_norm"], c.rms_eps)
-        k = rmsnorm(F.linear(x, L["wk"]), L["k_norm"], c.rms_eps)
-        v = F.linear(x, L["wv"])
+        q, k, v = F.linear(x, self.wqkv[i]).split([self.qd, self.kd, self.kd], dim=-1)
+        q, k = scaled_norm(q, L["q_norm"], c.rms_eps), scaled_norm(k, L["k_norm"], c.rms_eps)
         if c.clip_qkv is not None:
             q, k, v = (t.clamp(-c.clip_qkv, c.clip_qkv) for t in (q, k, v))
-        q = q.view(B, T, c.heads, c.head_dim).transpose(1, 2)
-        k = k.view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
-        v = v.view(B, T, c.kv_heads, c.head_dim).transpose(1, 2)
-        return q * cos + rotate_half(q) * sin, k * cos + rotate_half(k) * sin, v
+        heads = lambda t, n: t.reshape(B, T, n, c.head_dim).transpose(1, 2)
+        return rotate(heads(q, c.heads), cos, sin), rotate(heads(k, c.kv_heads), cos, sin), heads(v, c.kv_heads)
 
     def _attend(self, L, q, k, v, mask):
         c = self.c
         B, _, T, _ = q.shape
-        if c.kv_heads != c.heads:
-            k = k.repeat_interleave(c.heads // c.kv_heads, dim=1)
-            v = v.repeat_interleave(c.heads // c.kv_heads, dim=1)
-        a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask[:, None])
+        a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask[:, None], enable_gqa=c.kv_heads != c.heads)
         return F.linear(a.transpose(1, 2).reshape(B, T, c.heads * c.head_dim), L["wo"])
 
     # ---- prefill / general forward (shapes depend on the call)
@@ -186,21 +201,21 @@ class Decoder:
         diag = torch.zeros(T, start + T, dtype=torch.bool, device=dev)
         diag[torch.arange(T, device=dev), start + torch.arange(T, device=dev)] = True
         mask = mask | (~mask.any(-1, keepdim=True) & diag[None])  # a padding query attends to itself
-        cos, sin = self._rope(positions, W["embed"].dtype)
+        cos, sin = self.rope.at(positions)
         x = F.embedding(tokens, W["embed"])
         for i, L in enumerate(W["layers"]):
-            q, k, v = self._qkv(L, rmsnorm(x, L["attn_norm"], c.rms_eps), cos, sin)
+            q, k, v = self._qkv(i, scaled_norm(x, L["attn_norm"], c.rms_eps), cos, sin)
             if cache is not None:
                 cache.k[i][:, :, start:start + T] = k
                 cache.v[i][:, :, start:start + T] = v
                 k, v = cache.k[i][:, :, :start + T], cache.v[i][:, :, :start + T]
             x = x + self._attend(L, q, k, v, mask)
-            h = rmsnorm(x, L["mlp_norm"], c.rms_eps).reshape(B * T, -1)
+            h = scaled_norm(x, L["mlp_norm"], c.rms_eps).reshape(B * T, -1)
             x = x + self.moe(i, h).view(B, T, -1)
         if cache is not None:
             cache.length += T
             cache.next_pos += valid.long().sum(1)
-        return F.linear(rmsnorm(x, W["final_norm"], c.rms_eps), W["lm_head"])
+        return F.linear(scaled_norm(x, W["final_norm"], c.rms_eps), W["lm_head"])
 
     # ---- one decode step with fixed shapes (CUDA-graph capturable)
     @torch.no_grad()
@@ -213,19 +228,19 @@ class Decoder:
         onehot = torch.arange(cache.capacity, device=tokens.device) == slot          # [capacity]
         cache.valid.logical_or_(onehot[None])
         mask = cache.valid[:, None, :]                                                 # [B,1,capacity]
-        cos, sin = self._rope(cache.next_pos[:, None], W["embed"].dtype)
+        cos, sin = self.rope.at(cache.next_pos[:, None])
         x = F.embedding(tokens[:, None], W["embed"])
         at = slot.view(1)  # device index: the step stays replayable
         for i, L in enumerate(W["layers"]):
-            q, k, v = self._qkv(L, rmsnorm(x, L["attn_norm"], c.rms_eps), cos, sin)
+            q, k, v = self._qkv(i, scaled_norm(x, L["attn_norm"], c.rms_eps), cos, sin)
             cache.k[i].index_copy_(2, at, k)
             cache.v[i].index_copy_(2, at, v)
             x = x + self._attend(L, q, cache.k[i], cache.v[i], mask)
-            h = rmsnorm(x, L["mlp_norm"], c.rms_eps).reshape(B, -1)
+            h = scaled_norm(x, L["mlp_norm"], c.rms_eps).reshape(B, -1)
             x = x + self.moe(i, h).view(B, 1, -1)
         cache.length += 1
         cache.next_pos += 1
-        return F.linear(rmsnorm(x, W["final_norm"], c.rms_eps), W["lm_head"])[:, 0]
+        return F.linear(scaled_norm(x, W["final_norm"], c.rms_eps), W["lm_head"])[:, 0]
 
     @torch.no_grad()
     def generate(self, prompts, max_new_tokens, graph=False, marks=None, session=None):

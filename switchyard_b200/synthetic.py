@@ -43,17 +43,10 @@ def zipf_bias(experts=EXPERTS, alpha=ZIPF_ALPHA, s=ZIPF_S, seed=ZIPF_PERM_SEED):
 
 def biased_ops(mode, bias):
     """The expert-parallel operations with `bias` (float [E]) added to the router logits in the
-    logits' dtype before the routing kernel: how the benchmark applies the Zipf skew on every
-    rank identically."""
+    logits' dtype before the routing: how the benchmark applies the Zipf skew on every rank
+    identically."""
     from .ep import CudaOps
-    import torch.nn.functional as F
-
-    class BiasedOps(CudaOps):
-        def route(self, h, router, k, norm):
-            logits = F.linear(h, router) + bias.to(device=h.device, dtype=h.dtype)
-            return self.k.ext().route(logits.contiguous(), k, norm)
-
-    return BiasedOps(mode)
+    return CudaOps(mode, logit_bias=bias)
 
 
 def busiest_over_mean(idx, experts=EXPERTS):

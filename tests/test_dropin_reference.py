@@ -11,10 +11,11 @@ import pytest
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("SWITCHYARD_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+REF = next((c for c in (os.environ.get("SWITCHYARD_REFERENCE"), os.path.join(os.path.dirname(ROOT), "reference"),
+                        os.path.join(ROOT, "baseline", "_ref"))
+            if c and os.path.exists(os.path.join(c, "switchyard", "serve.py"))), None)
 
-pytestmark = pytest.mark.skipif(not os.path.exists(os.path.join(REF, "switchyard", "serve.py")),
-                                reason="no reference checkout available")
+pytestmark = pytest.mark.skipif(REF is None, reason="no reference checkout available")
 
 
 @pytest.fixture(scope="module")

@@ -67,6 +67,7 @@ def test_mailbox_contents_match_the_reference(golden, name):
             assert torch.equal(m["offsets"], T(golden[pre + "/offsets"]))
             assert torch.equal(m["counts"], T(golden[pre + "/counts"]))
             assert torch.equal(m["w"], T(golden[pre + "/w"]))
+            assert m["rows"] == m["x"].shape[0]
         assert [list(s) for s in sh["st"][d]["seg"]] == golden[f"ep/{name}/seg/{d}"].tolist()
 
 

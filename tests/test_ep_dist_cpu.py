@@ -2,8 +2,9 @@
 real processes over gloo, without a GPU: the device side is replaced by the host-memory mock of
 oracle/ep_dist_mock.py (windows in /dev/shm mapped by the peers, polling flag waits), so what
 runs is the product's own host logic: window layout, pointer tables, argument order, device-side
-epochs, mailbox reuse over several layers, a rank with zero tokens. Every rank's output must
-equal the one-process layer computed with the same row-at-a-time arithmetic."""
+epochs, mailbox reuse over several layers, a rank with zero tokens, a permuted expert placement.
+Every rank's output must equal the one-process layer computed with the same row-at-a-time
+arithmetic."""
 
 import socket
 
@@ -19,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, sizes_per_layer, fused, out):
+def _rank_main(rank, world, port, sizes_per_layer, placement, out):
     import torch.distributed as dist
     from oracle import ep_dist_mock as mock
     from switchyard_b200.ep_dist import DistributedExpertParallel
@@ -34,12 +35,20 @@ def _rank_main(rank, world, port, sizes_per_layer, fused, out):
         dn = (torch.randn(E, H, I, generator=g) * 0.3).half()
         per = E // world
         ep = DistributedExpertParallel(E, k, False, H, I, max_tokens=max(max(s) for s in sizes_per_layer),
-                                       dtype=torch.float16, mode="gemv", backend=backend, fused_transport=fused)
-        ok = True
+                                       dtype=torch.float16, mode="gemv", backend=backend, placement=placement)
+        # this rank's experts: a contiguous block, or its block of the placement
+        mine = list(range(rank * per, (rank + 1) * per)) if placement is None else placement[rank * per:(rank + 1) * per]
+        my_gu, my_dn = gu[mine].contiguous(), dn[mine].contiguous()
+        # the one-process comparand computes the same function; with a placement a token's expert
+        # outputs are added in placement order, so the comparand is given the permuted layer
+        order = list(range(E)) if placement is None else placement
+        ok, sent = True, 0
         for layer_no, sizes in enumerate(sizes_per_layer):
             h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).half()
-            got = ep.layer(h, router, gu[rank * per:(rank + 1) * per].contiguous(), dn[rank * per:(rank + 1) * per].contiguous())
-            ok = ok and torch.equal(got, mock.single_layer(h, router, gu, dn, k, False))
+            got = ep.layer(h, router, my_gu, my_dn)
+            ok = ok and torch.equal(got, mock.single_layer(h, router[order], gu[order], dn[order], k, False))
+        sent, kept = ep.row_counts()
+        ok = ok and sent + kept == sum(s[rank] for s in sizes_per_layer) * k
         ep.close()
         out.put((rank, ok, ""))
     except BaseException:
@@ -50,15 +59,18 @@ def _rank_main(rank, world, port, sizes_per_layer, fused, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,sizes,fused", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], True),
-                                               (2, [(5, 9), (0, 3), (1, 0)], False),
-                                               (4, [(3, 7, 0, 2), (8, 8, 8, 8)], True)])
-def test_protocol_over_gloo_processes(world, sizes, fused):
+PLACEMENT = [5, 12, 0, 9, 3, 14, 7, 1, 10, 2, 15, 6, 11, 4, 13, 8]
+
+
+@pytest.mark.parametrize("world,sizes,placement", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], None),
+                                                   (2, [(5, 9), (0, 3), (1, 0)], PLACEMENT),
+                                                   (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None)])
+def test_protocol_over_gloo_processes(world, sizes, placement):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, fused, out)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, placement, out)) for r in range(world)]
     for p in procs:
         p.start()
     results = [out.get(timeout=180) for _ in procs]
@@ -72,7 +84,7 @@ def test_protocol_over_gloo_processes(world, sizes, fused):
 def test_window_layout_is_aligned_and_disjoint():
     from switchyard_b200.ep_dist import window_layout
     lay = window_layout(8, 8, 2048, 2048, 2048, 2)
-    names = ["arrive", "ret", "done", "epoch", "meta", "w", "x", "y"]
+    names = ["arrive", "ret", "epoch", "counters", "stats", "meta", "w", "x", "y"]
     offs = [lay[n] for n in names] + [lay["total"]]
     assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
     assert lay["x"] - lay["w"] >= 8 * 2048 * 2 and lay["y"] - lay["x"] >= 8 * 2048 * 2048 * 2

@@ -1,9 +1,10 @@
 """The one-process-per-GPU expert-parallel layer (switchyard_b200.ep_dist) on real GPUs: every
 rank's output is bit-identical to the single-GPU layer run with the same mode on that rank's
-tokens. Needs at least two GPUs (kernels that wait for another rank's flag must not share a GPU
-with the kernels that set it); ranks are child processes, rendezvous on 127.0.0.1."""
+tokens. Ranks are child processes, rendezvous on 127.0.0.1. With one rank (every expert local,
+every row "sent" to the rank's own mailbox) the whole transport runs on a single GPU; with more
+ranks each needs its own GPU (kernels that wait for another rank's flag must not share a GPU
+with the kernels that set it)."""
 
-import os
 import socket
 
 import pytest
@@ -12,6 +13,9 @@ import torch
 import cases
 
 pytestmark = pytest.mark.gpu
+
+SMALL = dict(E=64, k=8, H=256, I=128, std=None)
+OLMOE = dict(E=64, k=8, H=2048, I=1024, std=0.02)   # the benchmark's layer
 
 
 def n_gpus():
@@ -24,39 +28,61 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out):
+def _worker(rank, world, port, sizes_per_layer, mode, dtype_name, shape, opts, out):
     try:
-        _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out)
+        _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, shape, opts, out)
     except BaseException:  # report instead of leaving the parent waiting for a result
         import traceback
         out.put((rank, False, traceback.format_exc()))
 
 
-def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out):
+def _weights(shape, dtype, device):
+    """The full layer, generated on the device from one seed (the same on every rank)."""
+    E, H, I = shape["E"], shape["H"], shape["I"]
+    g = torch.Generator(device=device).manual_seed(0)
+    rs, gs, ds = (0.2, H ** -0.5, I ** -0.5) if shape["std"] is None else (shape["std"],) * 3
+    router = (torch.randn(E, H, device=device, generator=g) * rs).to(dtype)
+    gu = torch.empty(E, 2 * I, H, dtype=dtype, device=device)
+    dn = torch.empty(E, H, I, dtype=dtype, device=device)
+    for e in range(E):
+        gu[e] = (torch.randn(2 * I, H, device=device, generator=g) * gs).to(dtype)
+        dn[e] = (torch.randn(H, I, device=device, generator=g) * ds).to(dtype)
+    return router, gu, dn
+
+
+def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, shape, opts, out):
     import torch.distributed as dist
-    from switchyard_b200 import kernels
+    from switchyard_b200 import kernels, synthetic
     from switchyard_b200.ep_dist import DistributedExpertParallel
     dtype = getattr(torch, dtype_name)
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
-        E, k, H, I = 64, 8, 256, 128
-        g = cases.gen(0)
-        router = (torch.randn(E, H, generator=g) * 0.2).to(dtype).cuda()
-        gu = (torch.randn(E, 2 * I, H, generator=g) * H ** -0.5).to(dtype).cuda()
-        dn = (torch.randn(E, H, I, generator=g) * I ** -0.5).to(dtype).cuda()
+        E, k, H, I = shape["E"], shape["k"], shape["H"], shape["I"]
+        router, gu, dn = _weights(shape, dtype, f"cuda:{rank}")
         per = E // world
-        my_gu, my_dn = gu[rank * per:(rank + 1) * per].contiguous(), dn[rank * per:(rank + 1) * per].contiguous()
+        placement = opts.get("placement")
+        mine = list(range(rank * per, (rank + 1) * per)) if placement is None else placement[rank * per:(rank + 1) * per]
+        my_gu, my_dn = gu[mine].contiguous(), dn[mine].contiguous()
+        order = list(range(E)) if placement is None else placement
+        bias = synthetic.zipf_bias(E) if opts.get("zipf") else None
         ep = DistributedExpertParallel(E, k, False, H, I, max_tokens=max(max(s) for s in sizes_per_layer), dtype=dtype,
-                                       mode=mode, fused_transport=fused)
-        ok = True
+                                       mode=mode, logit_bias=bias, placement=placement)
+        dbias = None if bias is None else bias.to("cuda").to(dtype)[order].contiguous()
+        # the comparand: the single-GPU layer with all experts in placement order (a token's
+        # expert outputs are then added in the same order on both sides)
+        r1, g1, d1 = router[order].contiguous(), gu[order].contiguous(), dn[order].contiguous()
+        ok, rows = True, 0
         for layer_no, sizes in enumerate(sizes_per_layer):
-            hs = [torch.randn(n, H, generator=cases.gen(100 * layer_no + r)).to(dtype) for r, n in enumerate(sizes)]
-            h = hs[rank].cuda()
+            h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).to(dtype).cuda()
             got = ep.layer(h, router, my_gu, my_dn)
-            want = kernels.moe_layer(h, router, gu, dn, k, False, mode)
+            srt = kernels.route_and_sort(h, r1, k, False, dbias)
+            want = kernels._sorted_experts(h, srt, g1, d1, k, ep.mode)
             torch.cuda.synchronize()
             ok = ok and torch.equal(got, want)
+            rows += sizes[rank] * k
+        sent, kept = ep.row_counts()
+        ok = ok and sent + kept == rows and (world > 1 or sent == 0)
         status = kernels.ext().device_status()
         ep.close()
         out.put((rank, ok, status))
@@ -64,18 +90,18 @@ def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, fused, out)
         dist.destroy_process_group()
 
 
-def run(world, sizes_per_layer, mode, dtype_name="float16", fused=True):
+def run(world, sizes_per_layer, mode, dtype_name="float16", shape=SMALL, **opts):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, sizes_per_layer, mode, dtype_name, fused, out))
+    procs = [ctx.Process(target=_worker, args=(r, world, port, sizes_per_layer, mode, dtype_name, shape, opts, out))
              for r in range(world)]
     for p in procs:
         p.start()
     results = []
     for _ in procs:
-        results.append(out.get(timeout=120))
+        results.append(out.get(timeout=300))
     for p in procs:
         p.join(timeout=30)
     for rank, ok, status in sorted(results, key=lambda r: r[0]):
@@ -83,6 +109,24 @@ def run(world, sizes_per_layer, mode, dtype_name="float16", fused=True):
         assert ok, f"rank {rank}: output differs from the single-GPU layer"
 
 
+# ---- one rank: the whole transport on a single GPU
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+@pytest.mark.parametrize("dtype_name", ["float16", "bfloat16"])
+def test_one_rank_equals_the_single_gpu_layer(mode, dtype_name):
+    run(1, [(1,), (7,), (0,), (200,), (64,), (333,)], mode, dtype_name)
+
+
+def test_one_rank_at_the_benchmark_shape():
+    run(1, [(64,), (256,), (8,)], "gemv", shape=OLMOE, zipf=True)
+    run(1, [(300,)], "gemm", shape=OLMOE, zipf=True)
+
+
+def test_one_rank_with_a_placement():
+    g = cases.gen(9)
+    run(1, [(50,), (3,)], "gemv", placement=torch.randperm(64, generator=g).tolist())
+
+
+# ---- several ranks, one GPU each
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("mode", ["gemv", "gemm"])
 def test_two_ranks_bit_identical(mode):
@@ -95,8 +139,17 @@ def test_two_ranks_bf16():
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
-def test_two_ranks_with_every_transport_step_as_its_own_launch():
-    run(2, [(7, 30), (0, 5), (64, 3)], "gemv", fused=False)
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+def test_two_ranks_at_the_benchmark_shape(mode):
+    """256 tokens per GPU at OLMoE's sizes with the Zipf-skewed routing (configs[2]); in the compute
+    shape also 2048 tokens per GPU: thousands of rows per rank through the mailbox ranges."""
+    run(2, [(256, 256), (64, 1)] + ([(2048, 2048)] if mode == "gemm" else []), mode, shape=OLMOE, zipf=True)
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
+def test_two_ranks_with_a_placement():
+    g = cases.gen(9)
+    run(2, [(50, 20), (3, 0)], "gemv", placement=torch.randperm(64, generator=g).tolist())
 
 
 @pytest.mark.skipif(n_gpus() < 4, reason="needs four GPUs")
@@ -108,3 +161,4 @@ def test_four_ranks_bit_identical(mode):
 @pytest.mark.skipif(n_gpus() < 8, reason="needs eight GPUs")
 def test_eight_ranks_bit_identical():
     run(8, [(3, 50, 0, 17, 1, 1, 64, 9), (256,) * 8], "gemv")
+    run(8, [(256,) * 8], "gemv", shape=OLMOE, zipf=True)

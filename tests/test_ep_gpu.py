@@ -1,7 +1,8 @@
 """The expert-parallel layer on GPUs: bit-identical to the one-GPU layer run with the same
 kernel mode on each rank's tokens. Cases follow the reference's tests/test_ep_cuda.py: several
-ranks sharing one GPU (streams, events, mailboxes and kernels without a second GPU), real
-peer-to-peer when more GPUs are visible, and the ordering of the layer after its caller."""
+ranks sharing one GPU (the window engine ordered by stream events: the same dispatch, expert and
+combine kernels without a second GPU), real peer-to-peer ordered by device-side flags when more
+GPUs are visible, and the ordering of the layer after its caller."""
 
 import pytest
 import torch
@@ -23,10 +24,10 @@ def weights(E=64, H=256, I=128, seed=0, dtype=torch.float16):
     return router.cuda(0), gu.cuda(0), dn.cuda(0)
 
 
-def run(devices, sizes, mode, E=64, k=8, dtype=torch.float16):
+def run(devices, sizes, mode, E=64, k=8, dtype=torch.float16, H=256, I=128):
     from switchyard_b200 import kernels
     from switchyard_b200.ep import CudaOps, ExpertParallel
-    router, gu, dn = weights(E, dtype=dtype)
+    router, gu, dn = weights(E, H, I, dtype=dtype)
     R, per = len(devices), E // len(devices)
     g = cases.gen(1)
     hs0 = [torch.randn(n, router.shape[1], generator=g).to(dtype).cuda(0) for n in sizes]
@@ -45,6 +46,12 @@ def run(devices, sizes, mode, E=64, k=8, dtype=torch.float16):
         assert torch.equal(t.to("cuda:0"), want)
         assert torch.equal(a.to("cuda:0"), want)
     assert kernels.ext().device_status("cuda:0") == 0
+    ep.check()
+    assert ep.windows and ep.host_ordered == (len(set(str(d) for d in devices)) < len(devices))
+    stats = ep.stats  # counted on the device, read here
+    assert stats["dispatched_rows"] + stats["local_rows"] == 3 * sum(sizes) * k
+    if R == 1:
+        assert stats["dispatched_rows"] == 0
     return ep
 
 
@@ -62,6 +69,66 @@ def test_four_and_eight_ranks_on_one_gpu(mode):
 
 def test_bf16_ranks_on_one_gpu():
     run(["cuda:0", "cuda:0"], (33, 12), "gemv", dtype=torch.bfloat16)
+
+
+def test_one_rank_and_growing_batches():
+    run(["cuda:0"], (40,), "gemv")
+    from switchyard_b200.ep import CudaOps, ExpertParallel
+    ep = ExpertParallel(["cuda:0", "cuda:0"], 64, 8, False, ops=CudaOps("gemv"))
+    ep.max_tokens = 8   # small windows: layer() must grow them; layer_rank() cannot and says so
+    router, gu, dn = weights(64)
+    args = ([router, router], [gu[:32].contiguous(), gu[32:].contiguous()], [dn[:32].contiguous(), dn[32:].contiguous()])
+    from switchyard_b200 import kernels
+    for n in (4, 20, 100, 7):
+        h = torch.randn(n, 256, generator=cases.gen(n)).half().cuda(0)
+        outs = ep.layer([h, h[: n // 2]], *args)
+        assert torch.equal(outs[0], kernels.moe_layer(h, router, gu, dn, 8, False, "gemv"))
+    assert ep.max_tokens == 128
+    big = torch.randn(200, 256, generator=cases.gen(1)).half().cuda(0)
+    with pytest.raises(RuntimeError, match="reserve"):
+        ep.phase_send(ep.new_state(), 0, big, router)
+    ep.reserve(200)
+    outs = ep.layer([big, big[:3]], *args)
+    assert torch.equal(outs[0], kernels.moe_layer(big, router, gu, dn, 8, False, "gemv"))
+
+
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+def test_two_ranks_at_the_benchmark_shape(mode):
+    """OLMoE's layer sizes (hidden 2048, width 1024), 256 tokens per rank; in the compute shape
+    2048 per rank as well."""
+    sizes = (256, 256) if mode == "gemv" else (2048, 300)
+    devices = ["cuda:0", "cuda:1"] if n_gpus() > 1 else ["cuda:0", "cuda:0"]
+    run(devices, sizes, mode, H=2048, I=1024)
+
+
+def test_capacity_factor_and_trace_on_the_gpu():
+    """Rows past an expert's capacity get weight 0 in token order; the counts come from the
+    device when stats is read. Against the layer computed with those weights zeroed by hand."""
+    import math
+    from switchyard_b200 import kernels
+    from switchyard_b200.ep import CudaOps, ExpertParallel
+    router, gu, dn = weights(64)
+    router[:4] += 0.5  # a few popular experts, so that the limit bites
+    ep = ExpertParallel(["cuda:0", "cuda:0"], 64, 8, False, ops=CudaOps("gemv"))
+    ep.capacity_factor, ep.trace = 1.0, []
+    hs = [torch.randn(n, 256, generator=cases.gen(n)).half().cuda(0) for n in (60, 33)]
+    outs = ep.layer(hs, [router, router], [gu[:32].contiguous(), gu[32:].contiguous()],
+                    [dn[:32].contiguous(), dn[32:].contiguous()])
+    dropped = 0
+    for h, o in zip(hs, outs):
+        idx, w = kernels.route(h, router, 8, False)
+        cap = math.ceil(1.0 * idx.numel() / 64)
+        w, seen = w.clone().cpu(), [0] * 64
+        for t in range(idx.shape[0]):
+            for s in range(8):
+                e = int(idx[t, s])
+                if seen[e] >= cap:
+                    w[t, s] = 0
+                    dropped += 1
+                seen[e] += 1
+        assert torch.equal(o, kernels.experts(h, idx, w.cuda(0), gu, dn, "gemv"))
+    assert dropped > 0 and ep.stats["dropped_rows"] == dropped and ep.stats["routed_rows"] == 93 * 8
+    assert len(ep.trace) == 2 and all(int(c.sum()) == n * 8 for (_, c), n in zip(ep.trace, (60, 33)))
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")

@@ -33,6 +33,11 @@ def K():
     assert kernels.ext().device_status(DEV) == 0  # no kernel gave up on a wait
 
 
+def force_tile(K, tile):
+    """0 = automatic, 1 = one CTA per tile, 2 = CTA pairs."""
+    assert K.ext().lib.sy_force_compute_tile(tile) == 0
+
+
 def ulp16(t):
     """Spacing of the 16-bit format at |t| (as float32)."""
     mant = 10 if t.dtype == torch.float16 else 7
@@ -89,6 +94,82 @@ def test_route_through_the_router_gemm(K):
     assert torch.equal(idx.cpu(), oidx)
 
 
+def test_route_never_leaves_the_expert_range(K):
+    """Rows of NaN, of -inf and of +inf have no valid softmax; the picks must still be experts
+    in [0, E) (the k lowest, weight 0 where nothing is valid), so that nothing downstream
+    indexes out of range."""
+    logits = cases.route_logits(64, 6).clone()
+    logits[1] = float("nan")
+    logits[2] = float("-inf")
+    logits[3, 5] = float("nan")
+    logits[4] = float("inf")
+    for norm in (False, True):
+        idx, w = K.ext().route(logits.to(DEV), 8, norm)
+        idx, w = idx.cpu(), w.cpu()
+        assert ((idx >= 0) & (idx < 64)).all()
+        for t in range(6):
+            assert len(set(idx[t].tolist())) == 8
+        assert idx[1].tolist() == list(range(8)) and idx[2].tolist() == list(range(8))
+        assert (w[1] == 0).all() and (w[2] == 0).all()
+        oidx, _ = mo.route_kernel_rule(logits[[0, 5]], 8, norm)
+        assert torch.equal(idx[[0, 5]], oidx)  # ordinary rows are untouched
+
+
+@pytest.mark.parametrize("N,E,k,H,dtype", [(1, 64, 8, 2048, torch.float16), (8, 64, 8, 2048, torch.float16),
+                                           (64, 64, 8, 2048, torch.float16), (37, 64, 8, 256, torch.bfloat16),
+                                           (200, 128, 8, 512, torch.float16), (50, 16, 4, 96, torch.float16),
+                                           (1024, 8, 2, 64, torch.float16)])
+def test_route_fused_is_the_kernel_rule_on_its_own_logits(K, N, E, k, H, dtype):
+    """Router GEMM + route + sort in one launch. Contract: the routing is the kernel rule applied
+    to the logits the launch writes out, the sort is sort_by_expert of that routing (both bit for
+    bit), and those logits are the library GEMM's up to the 16-bit rounding of a differently
+    ordered float32 sum. Against softmax + topk of the library GEMM's logits the reference's own
+    tie allowance applies (tests/test_kernels_cuda.py:28-38)."""
+    g = cases.gen(N + E)
+    h = torch.randn(N, H, generator=g).to(dtype).to(DEV)
+    router = (torch.randn(E, H, generator=g) * H ** -0.5 * 3).to(dtype).to(DEV)
+    bias = (torch.randn(E, generator=g) * 0.3).to(dtype).to(DEV)
+    for norm, b in ((False, None), (True, None), (False, bias)):
+        a = K.ext().route_fused(h, router, k, norm, b, logits=True)
+        again = K.ext().route_fused(h, router, k, norm, b, logits=True)
+        assert all(torch.equal(x, y) for x, y in zip(a, again))  # the ticket comes back to zero; same bits
+        idx, w, counts, offsets, token, wsorted, pos_of, logits = a
+        oidx, ow = mo.route_kernel_rule(logits.cpu(), k, norm)
+        assert torch.equal(idx.cpu(), oidx)
+        assert ((w.cpu().float() - ow.float()).abs() <= ulp16(ow)).all()
+        for got, want in zip((counts, offsets, token, wsorted, pos_of), K.ext().sort_by_expert(idx, w, E)):
+            assert torch.equal(got, want)
+        lib = torch.nn.functional.linear(h, router)
+        if b is not None:
+            lib = lib + b
+        assert ((logits.float() - lib.float()).abs() <= 2 * ulp16(lib) + 2e-5).all()
+        if b is None and not norm:
+            probs = torch.softmax(lib.float(), -1).cpu()
+            ridx = probs.topk(k, -1).indices
+            same = (idx.cpu().long().sort(-1).values == ridx.sort(-1).values).all(-1)
+            for t in torch.nonzero(~same).flatten().tolist():
+                mine, ref = set(idx[t].tolist()), set(ridx[t].tolist())
+                gap = (probs[t, list(mine - ref)].sum() - probs[t, list(ref - mine)].sum()).abs().item()
+                # only near-ties may differ: logits one 16-bit step apart
+                assert gap < (0.02 if dtype == torch.float16 else 0.12) * probs[t, list(ref - mine)].sum().item()
+            assert same.float().mean().item() >= (0.97 if dtype == torch.float16 else 0.9)
+    assert K.ext().device_status() == 0
+
+
+def test_route_fused_rows_do_not_depend_on_the_batch(K):
+    """A token's logits (and so its routing) depend on its own row only: the same token routed
+    alone, in a batch of 64 and at another position gives identical bits."""
+    g = cases.gen(77)
+    h = torch.randn(64, 2048, generator=g).half().to(DEV)
+    router = (torch.randn(64, 2048, generator=g) * 0.02).half().to(DEV)
+    full = K.ext().route_fused(h, router, 8, False, logits=True)
+    for t in (0, 17, 63):
+        one = K.ext().route_fused(h[t:t + 1].contiguous(), router, 8, False, logits=True)
+        assert torch.equal(one[7][0], full[7][t]) and torch.equal(one[0][0], full[0][t]) and torch.equal(one[1][0], full[1][t])
+    rolled = K.ext().route_fused(torch.roll(h, 5, 0).contiguous(), router, 8, False, logits=True)
+    assert torch.equal(torch.roll(full[7], 5, 0), rolled[7])
+
+
 # ------------------------------------------------------------------------------ sort
 @pytest.mark.parametrize("name", list(cases.SORT_CASES))
 def test_sort_matches_the_reference_bit_for_bit(K, golden, name):
@@ -119,6 +200,34 @@ def test_sort_bf16_weights(K):
     want = mo.sort_by_expert(idx, w, 64)
     for got, ref in zip(a, want):
         assert torch.equal(got.cpu(), ref)
+
+
+@pytest.mark.parametrize("N", [40, 3000])
+def test_an_expert_id_out_of_range_is_skipped_everywhere(K, N):
+    """A choice whose expert id is outside [0, E) gets no row: the sort leaves it out of the
+    counts, marks pos_of with -1 and sets status 6; the combine adds nothing for it. No kernel
+    reads through the bad index."""
+    E, k, H = 64, 8, 256
+    idx, w = cases.sort_inputs(E, k, N, 21)
+    bad = idx.clone()
+    bad[3, 2], bad[N - 1, 0], bad[N // 2, 7] = 1 << 30, -5, E
+    counts, offsets, token, wsorted, pos_of = K.ext().sort_by_expert(bad.to(DEV), w.to(DEV), E)
+    assert K.ext().device_status() == 6
+    flat = bad.flatten()
+    valid = (flat >= 0) & (flat < E)
+    assert int(counts.sum()) == int(valid.sum()) == N * k - 3 and int(offsets[-1]) == N * k - 3
+    assert (pos_of.cpu()[~valid] == -1).all() and (pos_of.cpu()[valid] >= 0).all()
+    assert torch.equal(counts.cpu().long(), torch.bincount(flat[valid].long(), minlength=E))
+    y = torch.randn(N * k, H, generator=cases.gen(5)).half()
+    got = K.ext().combine(y.to(DEV), pos_of, bad.to(DEV), N).cpu()
+    rows = pos_of.cpu().view(N, k)
+    for t in (3, N - 1, N // 2, 0):
+        order = sorted((int(bad[t, j]), j) for j in range(k) if rows[t, j] >= 0)
+        acc = torch.zeros(H)
+        for _, j in order:
+            acc += y[rows[t, j]].float()
+        assert torch.equal(got[t], acc.half())
+    assert K.ext().device_status() == 0
 
 
 @pytest.mark.parametrize("N,E,k,dtype", [(1, 64, 8, torch.float16), (64, 64, 8, torch.float16), (300, 128, 8, torch.bfloat16),
@@ -199,7 +308,8 @@ def test_sizes_that_fill_no_tile(K, mode, N):
 def test_empty_experts_and_a_single_token(K):
     h, router, gu, dn = cases.layer_inputs(1)
     out = K.moe_layer(h.to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False)
-    ridx, rw = mo.route_reference(h, router, 8, False)
+    ridx, rw = mo.route_kernel_rule(K.ext().route_fused(h.to(DEV), router.to(DEV), 8, False, logits=True)[7].cpu(), 8, False)
+    ridx = ridx.long()
     want = mo.experts_reference(h.float(), ridx, rw.float(), gu.float(), dn.float())
     assert (out.float().cpu() - want).abs().max().item() < 2e-3
     out0 = K.moe_layer(h[:0].to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False)
@@ -258,12 +368,35 @@ def test_fused_ffn_equals_the_two_grouped_calls(K, mode, N, skew):
     for _ in range(3):
         got = K.ffn(hd, tok, off, counts.to(DEV), ws, gud, dnd, M, mode)
         assert torch.equal(got, want)
+    if mode == "gemv":
+        # ... and with the combine folded into the down projection's epilogue: the bits of combine()
+        out = E.combine(want, pos_of.to(DEV), ridx.int().to(DEV), N)
+        for _ in range(3):
+            got = E.expert_ffn_combine(hd, tok, gud, dnd, off, ws, pos_of.to(DEV), 8)
+            assert torch.equal(got, out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("N,E,k,H,I", [(64, 64, 8, 2048, 1024), (5, 16, 4, 200, 72), (130, 8, 2, 256, 128), (1, 64, 8, 2048, 1024)])
+def test_fused_combine_equals_the_combine_kernel(K, dtype, N, E, k, H, I):
+    """expert_ffn_combine against expert_ffn + combine at the benchmark's shape and at sizes that
+    fill no tile (hidden 200: a ragged last column block), with many rows per expert (E=8)."""
+    h, router, gu, dn = cases.layer_inputs(N, E=E, k=k, H=H, I=I, seed=4, skew=1.0, dtype=dtype)
+    ridx, rw = mo.route_reference(h, router, k, False)
+    counts, offsets, token, wsorted, pos_of = (t.to(DEV) for t in mo.sort_by_expert(ridx.int(), rw, E))
+    hd, gud, dnd = h.to(DEV), gu.to(DEV), dn.to(DEV)
+    X = K.ext()
+    y = X.expert_ffn(hd, token, gud, dnd, offsets, N * k, wsorted, 0)
+    want = X.combine(y, pos_of, ridx.int().to(DEV), N)
+    for _ in range(2):
+        assert torch.equal(X.expert_ffn_combine(hd, token, gud, dnd, offsets, wsorted, pos_of, k), want)
+    assert X.device_status() == 0
 
 
 @pytest.mark.parametrize("N,skew,dtype", [(64, 0.0, torch.float16), (333, 2.0, torch.float16), (2048, 2.0, torch.float16),
                                           (3000, 1.0, torch.bfloat16)])
-def test_compute_tiles_and_row_sources_agree_bit_for_bit(K, monkeypatch, N, skew, dtype):
-    """The compute shape has two tiles (one CTA; a CTA pair, SY_GEMM_TILE=pair) and two ways to
+def test_compute_tiles_and_row_sources_agree_bit_for_bit(K, N, skew, dtype):
+    """The compute shape has two tiles (one CTA; a CTA pair, sy_force_compute_tile) and two ways to
     fetch token rows (gathered through a_rows; contiguous rows by TMA). All four combinations
     run the same MMAs in the same k order: identical bits, separately and fused."""
     h, router, gu, dn = cases.layer_inputs(N, skew=skew, dtype=dtype)
@@ -275,15 +408,18 @@ def test_compute_tiles_and_row_sources_agree_bit_for_bit(K, monkeypatch, N, skew
     E = K.ext()
     hs = hd[tok.long()].contiguous()
     want_act = want = None
-    for tile in ("single", "pair"):
-        monkeypatch.setenv("SY_GEMM_TILE", tile)
-        for x, rows in ((hd, tok), (hs, None)):
-            act = E.grouped_gemm(x, rows, gud, off, None, 0, M, True, None)
-            y = E.grouped_gemm(act, None, dnd, off, None, 0, M, False, ws)
-            fused = E.expert_ffn(x, rows, gud, dnd, off, M, ws, 1)
-            if want is None:
-                want_act, want = act, y
-            assert torch.equal(act, want_act) and torch.equal(y, want) and torch.equal(fused, want)
+    try:
+        for tile in (1, 2):
+            force_tile(K, tile)
+            for x, rows in ((hd, tok), (hs, None)):
+                act = E.grouped_gemm(x, rows, gud, off, None, 0, M, True, None)
+                y = E.grouped_gemm(act, None, dnd, off, None, 0, M, False, ws)
+                fused = E.expert_ffn(x, rows, gud, dnd, off, M, ws, 1)
+                if want is None:
+                    want_act, want = act, y
+                assert torch.equal(act, want_act) and torch.equal(y, want) and torch.equal(fused, want)
+    finally:
+        force_tile(K, 0)
     assert E.device_status() == 0
 
 
@@ -305,7 +441,8 @@ def test_olmoe_decode_layer(K, olmoe, tokens, mode):
     h = synthetic.hidden_states(tokens, "cpu", torch.float16, seed=1)
     rd, gud, dnd = router.to(DEV), gu.to(DEV), dn.to(DEV)
     out = K.moe_layer(h.to(DEV), rd, gud, dnd, 8, False, mode).cpu()
-    logits = torch.nn.functional.linear(h.to(DEV), rd).cpu()
+    # the layer routes these sizes with route_fused: the oracle gets the logits that launch computes
+    logits = K.ext().route_fused(h.to(DEV), rd, 8, False, logits=True)[7].cpu()
     idx, w = mo.route_kernel_rule(logits, 8, False)
     want = mo.experts_reference(h.float(), idx.long(), w.float(), gu.float(), dn.float())
     loop16 = mo.experts_reference(h, idx.long(), w, gu, dn)
@@ -317,26 +454,28 @@ def test_olmoe_decode_layer(K, olmoe, tokens, mode):
 
 
 # ------------------------------------------------------------------------------ transport
-@pytest.mark.parametrize("tokens,dtype", [(4096, torch.bfloat16), (2048, torch.float16)])
+@pytest.mark.parametrize("tokens,dtype", [(1024, torch.bfloat16), (4096, torch.bfloat16), (8192, torch.bfloat16),
+                                          (2048, torch.float16)])
 def test_olmoe_prefill_layer_at_full_size(K, olmoe, tokens, dtype):
-    """The prefill configuration at its real size (hidden 2048, 64 experts of width 1024, top-8,
+    """The prefill configuration at its real sizes (hidden 2048, 64 experts of width 1024, top-8,
     Zipf-skewed routing: the busiest expert gets about four times the mean), checked on a sample
-    of tokens against the float32 expert loop; both compute tiles must give the same bits."""
-    import os
+    of tokens against the float32 expert loop. The tile is first the library's own choice (one
+    CTA below 768 rows per expert on average, CTA pairs from there: 8192 tokens take pairs), then
+    each tile forced: all three must give the same bits."""
     from switchyard_b200 import synthetic
     router, gu, dn = (t.to(dtype) for t in olmoe)
     h = synthetic.hidden_states(tokens, "cpu", dtype, seed=tokens)
     rd, gud, dnd, hd = router.to(DEV), gu.to(DEV), dn.to(DEV), h.to(DEV)
     logits = (torch.nn.functional.linear(hd, rd) + synthetic.zipf_bias().to(DEV).to(dtype)).contiguous()
     idx, w = K.ext().route(logits, 8, False)
-    outs = []
-    for tile in ("single", "pair"):
-        os.environ["SY_GEMM_TILE"] = tile
-        try:
+    outs = [K.experts(hd, idx, w, gud, dnd, "gemm")]
+    try:
+        for tile in (1, 2):
+            force_tile(K, tile)
             outs.append(K.experts(hd, idx, w, gud, dnd, "gemm"))
-        finally:
-            os.environ.pop("SY_GEMM_TILE", None)
-    assert torch.equal(outs[0], outs[1])
+    finally:
+        force_tile(K, 0)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert K.ext().device_status() == 0
     counts = torch.bincount(idx.flatten().long().cpu(), minlength=64)
     assert counts.max().item() > 3 * counts.float().mean().item()  # the skew is there
@@ -367,6 +506,38 @@ def test_graphed_layer_replays_the_same_bits(K):
             torch.cuda.synchronize()
             assert torch.equal(out, want.cpu())
     assert len(layer.graphs) == 3
+    layer.check()  # no replayed kernel gave up on a wait
+
+
+def test_a_wait_that_runs_out_ends_in_a_status_code(K):
+    """The bounded-wait path, exercised without hanging anything: a one-block kernel waits for a
+    flag that nothing sets, with the limit lowered to 2 ms. It returns by itself, the status word
+    reads 5 (a flag never came), sy_device_status answers SY_ERR_DEVICE, check_device raises, and
+    the next layer on the same stream runs and is correct."""
+    X = K.ext()
+    flags = torch.zeros(4, dtype=torch.int32, device=DEV)
+    epoch = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    default = X.lib.sy_wait_limit_ns()
+    assert default == 2_000_000_000
+    try:
+        X.set_wait_limit(0.002)
+        assert X.lib.sy_wait_limit_ns() == 2_000_000
+        assert X.lib.sy_ep_wait(flags.data_ptr(), 4, epoch.data_ptr(), 1, stream) == 0  # waits for flags >= 1
+        assert X.device_status() == 5
+        assert X.device_status() == 0  # reading clears it
+        X.lib.sy_ep_wait(flags.data_ptr(), 4, epoch.data_ptr(), 1, stream)
+        with pytest.raises(RuntimeError, match="device status 5"):
+            X.check_device()
+        flags.fill_(1)
+        assert X.lib.sy_ep_wait(flags.data_ptr(), 4, epoch.data_ptr(), 1, stream) == 0  # the flags are there: no timeout
+        assert X.device_status() == 0
+    finally:
+        X.lib.sy_set_wait_limit_ns(default)
+    h, router, gu, dn = cases.layer_inputs(9)
+    got = K.moe_layer(h.to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False, "gemv")
+    again = K.moe_layer(h.to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False, "gemv")
+    assert torch.equal(got, again) and X.device_status() == 0
 
 
 def test_gather_rows_and_copy(K):
