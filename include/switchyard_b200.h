@@ -76,13 +76,15 @@ int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int top_k, int n
                       void* scratch, size_t scratch_bytes, void* stream);
 
 /* route_sort — sy_route followed by sy_sort_by_expert in ONE launch, for decode-sized batches
- * (n_tokens * top_k <= sy_route_sort_max_choices() = 8192, n_experts <= 128): one block routes all
- * tokens and then sorts the choices it has just written. Outputs are those of the two separate
- * calls, bit for bit (moe_kernels.cu:73-89 and 142-157 in one step). */
+ * (n_tokens * top_k <= sy_route_sort_max_choices() = 8192, n_experts <= 128): blocks of sixteen
+ * tokens route a token per warp, and the block that finishes last sorts all choices. Outputs are
+ * those of the two separate calls, bit for bit (moe_kernels.cu:73-89 and 142-157 in one step).
+ * ticket: one zero-initialised int32 of device memory, left at zero (may be NULL up to sixteen
+ * tokens); launches that share it must not overlap. */
 int sy_route_sort_max_choices(void);
 int sy_route_sort(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
                   int32_t* idx, void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
-                  int32_t* pos_of, void* stream);
+                  int32_t* pos_of, int32_t* ticket, void* stream);
 
 /* route_fused — router GEMM, sy_route and sy_sort_by_expert in ONE launch for decode-sized
  * batches: replaces `F.linear(h, router)` followed by `route` (switchyard/kernels.py:30-32,

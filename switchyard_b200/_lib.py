@@ -29,7 +29,7 @@ SYMBOLS = {
                                   c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "sy_route_sort_max_choices": (c_int, []),
     "sy_route_sort": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_void_p, c_void_p, c_void_p, c_void_p]),
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "sy_route_fused_max_tokens": (c_int, []),
     "sy_route_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -160,51 +160,9 @@ sort_single_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, 
   scatter_chunk<T>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
 }
 
-// Decode-sized batches: routing and the sort in ONE block and one launch. The block's warps
-// route the tokens (same arithmetic as route_kernel), the block synchronises, and the sort
-// proceeds on the indices it has just written. Saves a launch where launches are what the
-// layer's small kernels cost.
-template <typename T>
-__global__ void __launch_bounds__(SORT_THREADS)
-route_sort_kernel(const T* __restrict__ logits, int n_tokens, int E, int k, int norm, int per_block, int* idx, T* w,
-                  int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ token,
-                  T* __restrict__ wsorted, int* __restrict__ pos_of, int* status) {
-  extern __shared__ int sh[];
-  int* wcount = sh;                       // [SORT_WARPS][E]
-  int* total = wcount + SORT_WARPS * E;   // [E]
-  int* off = total + E;                   // [E + 1]
-  const int per_warp = per_block / SORT_WARPS;
-  const int m = n_tokens * k;
-  pdl_launch_dependents();
-  pdl_wait();  // the logits come from the router GEMM before this kernel
-  for (int t = threadIdx.x >> 5; t < n_tokens; t += SORT_WARPS)
-    route_token_any<T>(logits + (size_t)t * E, E, k, norm, threadIdx.x & 31, idx + (size_t)t * k, w + (size_t)t * k);
-  __syncthreads();  // the block's own global writes are visible to the block after the barrier
-  count_chunk(idx, m, 0, per_warp, E, wcount);
-  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
-    int s = 0;
-    for (int wi = 0; wi < SORT_WARPS; ++wi) s += wcount[wi * E + e];
-    total[e] = s;
-    counts[e] = s;
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) warp_scan_experts(total, E, off);
-  __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += SORT_THREADS) offsets[e] = off[e];
-  for (int e = threadIdx.x; e < E; e += SORT_THREADS) {
-    int at = off[e];
-    for (int wi = 0; wi < SORT_WARPS; ++wi) {
-      int c = wcount[wi * E + e];
-      wcount[wi * E + e] = at;
-      at += c;
-    }
-  }
-  __syncthreads();
-  scatter_chunk<T>(idx, w, m, k, 0, per_warp, E, wcount, token, wsorted, pos_of, status);
-}
-
-// Decode-sized batches, everything before the experts in ONE launch: the router GEMM, the
-// routing and the sort. A block owns sixteen tokens. Its sixteen warps each take every
+// Decode-sized batches, everything before the experts in ONE launch: the router GEMM (optional:
+// with `logits_in` the logits are taken as given and only the routing and the sort run, which is
+// sy_route_sort), the routing and the sort. A block owns sixteen tokens. Its sixteen warps each take every
 // sixteenth 32-wide slice of the hidden dimension and multiply the sixteen token rows by all
 // E router rows over their slices with warp-level MMAs (the operands come straight from global
 // memory, 16 bytes per lane and row: a lane's eight consecutive k feed two MMAs, and because
@@ -221,7 +179,8 @@ constexpr int RF_TOKENS = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(SORT_THREADS)
-route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const T* __restrict__ bias, int n_tokens, int E,
+route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const T* __restrict__ bias,
+                   const T* __restrict__ logits_in, int n_tokens, int E,
                    int K, int k, int norm, int per_block, T* __restrict__ logits_out, int* idx, T* w, int* __restrict__ counts,
                    int* __restrict__ offsets, int* __restrict__ token, T* __restrict__ wsorted, int* __restrict__ pos_of,
                    int* ticket, int* status) {
@@ -233,8 +192,14 @@ route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const 
   const int t0 = blockIdx.x * RF_TOKENS;
   const int n_tiles = E >> 3;  // eight experts per MMA
   pdl_launch_dependents();
-  pdl_wait();  // the hidden states come from the caller's previous kernel
+  pdl_wait();  // the hidden states (or the logits) come from the caller's previous kernel
 
+  if (logits_in) {
+    // the logits are given (sy_route_sort): a warp per token straight from global memory
+    if (t0 + warp < n_tokens)
+      route_token_any<T>(logits_in + (size_t)(t0 + warp) * E, E, k, norm, lane, idx + (size_t)(t0 + warp) * k,
+                         w + (size_t)(t0 + warp) * k);
+  } else {
   // ---- router GEMM: this warp's slices of k
   float acc[ROUTE_MAX_E / 8][4];
 #pragma unroll
@@ -294,6 +259,7 @@ route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const 
   // ---- routing: a warp per token
   if (t0 + warp < n_tokens)
     route_token_any<T>(partial + warp * E, E, k, norm, lane, idx + (size_t)(t0 + warp) * k, w + (size_t)(t0 + warp) * k);
+  }
   // ---- the last block to get here sorts every block's choices
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -447,9 +413,52 @@ extern "C" int sy_sort_by_expert(const int32_t* idx, const void* w, int m, int t
 
 extern "C" int sy_route_sort_max_choices(void) { return sy::SORT_SINGLE_MAX; }
 
+namespace sy {
+// Shared launch of sy_route_sort (logits given) and sy_route_fused (router GEMM inside).
+static int launch_route_fused(const void* h, const void* router, const void* bias, const void* logits_in, int n_tokens,
+                              int n_experts, int hidden, int top_k, int norm, int dtype, void* logits_out, int32_t* idx,
+                              void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted, int32_t* pos_of,
+                              int32_t* ticket, void* stream) {
+  int* status = device_status_word();
+  if (!status) return SY_ERR_CUDA;
+  const int m = n_tokens * top_k;
+  const SortShape sh = sort_shape(m);
+  const size_t sort_smem = (size_t)(SORT_WARPS * n_experts + 3 * n_experts + 1) * sizeof(int);
+  const size_t gemm_smem = logits_in ? 0 : (size_t)SORT_WARPS * RF_TOKENS * n_experts * sizeof(float);
+  const size_t smem = sort_smem > gemm_smem ? sort_smem : gemm_smem;
+  const int blocks = (n_tokens + RF_TOKENS - 1) / RF_TOKENS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  static std::atomic<int> configured[MAX_DEVICES][2];
+  int dev = 0;
+  SY_CUDA(cudaGetDevice(&dev));
+  const int which = dtype == SY_DTYPE_F16 ? 0 : 1;
+  if (!configured[dev][which].load(std::memory_order_acquire)) {
+    const size_t most = (size_t)SORT_WARPS * RF_TOKENS * ROUTE_MAX_E * sizeof(float);
+    if (which == 0)
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+    else
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+    configured[dev][which].store(1, std::memory_order_release);
+  }
+  if (dtype == SY_DTYPE_F16)
+    return launch_kernel(route_fused_kernel<__half>, blocks, SORT_THREADS, smem, s, "route_fused launch",
+                         static_cast<const __half*>(h), static_cast<const __half*>(router),
+                         static_cast<const __half*>(bias), static_cast<const __half*>(logits_in), n_tokens, n_experts,
+                         hidden, top_k, norm, sh.per_block, static_cast<__half*>(logits_out), idx,
+                         static_cast<__half*>(w), counts, offsets, token, static_cast<__half*>(wsorted), pos_of, ticket,
+                         status);
+  return launch_kernel(route_fused_kernel<__nv_bfloat16>, blocks, SORT_THREADS, smem, s, "route_fused launch",
+                       static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(router),
+                       static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(logits_in), n_tokens,
+                       n_experts, hidden, top_k, norm, sh.per_block, static_cast<__nv_bfloat16*>(logits_out), idx,
+                       static_cast<__nv_bfloat16*>(w), counts, offsets, token, static_cast<__nv_bfloat16*>(wsorted),
+                       pos_of, ticket, status);
+}
+}  // namespace sy
+
 extern "C" int sy_route_sort(const void* logits, int n_tokens, int n_experts, int top_k, int norm_topk_prob, int dtype,
                              int32_t* idx, void* w, int32_t* counts, int32_t* offsets, int32_t* token, void* wsorted,
-                             int32_t* pos_of, void* stream) {
+                             int32_t* pos_of, int32_t* ticket, void* stream) {
   using namespace sy;
   SY_REQUIRE(n_tokens >= 1 && n_experts >= 1 && n_experts <= 128 && top_k >= 1 && top_k <= 8 && top_k <= n_experts,
              "route_sort: 1..128 experts, top-8, at least one token (got N=%d, E=%d, k=%d)", n_tokens, n_experts, top_k);
@@ -457,21 +466,9 @@ extern "C" int sy_route_sort(const void* logits, int n_tokens, int n_experts, in
              SORT_SINGLE_MAX, (long long)n_tokens * top_k);
   SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "route_sort: dtype must be f16 or bf16");
   SY_REQUIRE(logits && idx && w && counts && offsets && token && wsorted && pos_of, "route_sort: null pointer");
-  int* status = device_status_word();
-  if (!status) return SY_ERR_CUDA;
-  const int m = n_tokens * top_k;
-  const SortShape sh = sort_shape(m);
-  const size_t smem = (size_t)(SORT_WARPS * n_experts + 3 * n_experts + 1) * sizeof(int);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == SY_DTYPE_F16)
-    return launch_kernel(route_sort_kernel<__half>, 1, SORT_THREADS, smem, s, "route_sort launch",
-                         static_cast<const __half*>(logits), n_tokens, n_experts, top_k, norm_topk_prob, sh.per_block,
-                         idx, static_cast<__half*>(w), counts, offsets, token, static_cast<__half*>(wsorted), pos_of,
-                         status);
-  return launch_kernel(route_sort_kernel<__nv_bfloat16>, 1, SORT_THREADS, smem, s, "route_sort launch",
-                       static_cast<const __nv_bfloat16*>(logits), n_tokens, n_experts, top_k, norm_topk_prob,
-                       sh.per_block, idx, static_cast<__nv_bfloat16*>(w), counts, offsets, token,
-                       static_cast<__nv_bfloat16*>(wsorted), pos_of, status);
+  SY_REQUIRE(ticket || n_tokens <= RF_TOKENS, "route_sort: more than %d tokens need a ticket", RF_TOKENS);
+  return launch_route_fused(nullptr, nullptr, nullptr, logits, n_tokens, n_experts, 0, top_k, norm_topk_prob, dtype,
+                            nullptr, idx, w, counts, offsets, token, wsorted, pos_of, ticket, stream);
 }
 
 extern "C" int sy_route_fused_max_tokens(void) { return sy::SORT_SINGLE_MAX / 8; }
@@ -492,38 +489,8 @@ extern "C" int sy_route_fused(const void* h, const void* router, const void* bia
   SY_REQUIRE(h && router && idx && w && counts && offsets && token && wsorted && pos_of && ticket,
              "route_fused: null pointer");
   SY_REQUIRE(((uintptr_t)h % 16 == 0) && ((uintptr_t)router % 16 == 0), "route_fused: h and router must be 16-byte aligned");
-  int* status = device_status_word();
-  if (!status) return SY_ERR_CUDA;
-  const int m = n_tokens * top_k;
-  const SortShape sh = sort_shape(m);
-  const size_t sort_smem = (size_t)(SORT_WARPS * n_experts + 3 * n_experts + 1) * sizeof(int);
-  const size_t gemm_smem = (size_t)SORT_WARPS * RF_TOKENS * n_experts * sizeof(float);
-  const size_t smem = sort_smem > gemm_smem ? sort_smem : gemm_smem;
-  const int blocks = (n_tokens + RF_TOKENS - 1) / RF_TOKENS;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  static std::atomic<int> configured[MAX_DEVICES][2];
-  int dev = 0;
-  SY_CUDA(cudaGetDevice(&dev));
-  const int which = dtype == SY_DTYPE_F16 ? 0 : 1;
-  if (!configured[dev][which].load(std::memory_order_acquire)) {
-    const size_t most = (size_t)SORT_WARPS * RF_TOKENS * ROUTE_MAX_E * sizeof(float);
-    if (which == 0)
-      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
-    else
-      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
-    configured[dev][which].store(1, std::memory_order_release);
-  }
-  if (dtype == SY_DTYPE_F16)
-    return launch_kernel(route_fused_kernel<__half>, blocks, SORT_THREADS, smem, s, "route_fused launch",
-                         static_cast<const __half*>(h), static_cast<const __half*>(router),
-                         static_cast<const __half*>(bias), n_tokens, n_experts, hidden, top_k, norm_topk_prob,
-                         sh.per_block, static_cast<__half*>(logits_out), idx, static_cast<__half*>(w), counts, offsets,
-                         token, static_cast<__half*>(wsorted), pos_of, ticket, status);
-  return launch_kernel(route_fused_kernel<__nv_bfloat16>, blocks, SORT_THREADS, smem, s, "route_fused launch",
-                       static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(router),
-                       static_cast<const __nv_bfloat16*>(bias), n_tokens, n_experts, hidden, top_k, norm_topk_prob,
-                       sh.per_block, static_cast<__nv_bfloat16*>(logits_out), idx, static_cast<__nv_bfloat16*>(w), counts,
-                       offsets, token, static_cast<__nv_bfloat16*>(wsorted), pos_of, ticket, status);
+  return launch_route_fused(h, router, bias, nullptr, n_tokens, n_experts, hidden, top_k, norm_topk_prob, dtype, logits_out,
+                            idx, w, counts, offsets, token, wsorted, pos_of, ticket, stream);
 }
 
 // ---- sort_by_expert_static: the same sort for callers that cannot hand over scratch ----------

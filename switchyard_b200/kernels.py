@@ -15,12 +15,16 @@ Differences a caller can observe:
   * there is no cuBLAS mode; "cublas" is accepted as an alias of "gemm";
   * `experts(mode="auto")` chooses from the token count, not from a device-to-host read of
     the largest expert's row count, so the layer never synchronises;
-  * `moe_layer` with at most ROUTE_FUSED_MAX_TOKENS tokens computes the router logits inside the
-    routing launch (`route_fused`) instead of calling the library GEMM: the logits are the same
-    dot products summed in another order, so they can differ from `F.linear`'s in the last bit
-    and a token whose k-th and (k+1)-th logits are that close may pick the other expert.
-    `route(h, router, ...)` keeps the library GEMM, as in the reference.
+  * `route_fused` computes the router logits inside the routing launch instead of calling the
+    library GEMM. It is not what `moe_layer` uses unless SWITCHYARD_FUSED_ROUTER=1 (or
+    `route_and_sort(..., fused=True)`): measured on a B200 the library GEMM followed by the
+    one-launch route + sort is faster (10 us against 14-17 us up to 64 tokens), and the fused
+    logits, the same dot products summed in another order, can differ from the library's in the
+    last bit, so that a token whose k-th and (k+1)-th logits are that close may pick the other
+    expert.
 """
+
+import os
 
 import ctypes
 
@@ -218,7 +222,7 @@ class Ext:
                        "sort_by_expert")
         return [counts, offsets, token, wsorted, pos_of]
 
-    def route_sort(self, logits, k, norm):
+    def route_sort(self, logits, k, norm, scratch=None):
         """route + sort_by_expert in one launch (decode-sized batches): returns
         [idx, w, counts, offsets, token, wsorted, pos_of], the same tensors the two calls give."""
         _check(logits, "logits")
@@ -232,9 +236,10 @@ class Ext:
         halves = torch.empty(2 * M, dtype=logits.dtype, device=dev)
         w, wsorted = halves[:M].view(N, k), halves[M:]
         with _Device(dev) as stream:
+            ticket = (scratch or self.scratch(dev, stream)).ticket
             _lib.check(self.lib.sy_route_sort(_ptr(logits), N, E, int(k), int(bool(norm)), code, _ptr(idx), _ptr(w),
                                               _ptr(counts), _ptr(offsets), _ptr(token), _ptr(wsorted), _ptr(pos_of),
-                                              stream), "route_sort")
+                                              _ptr(ticket), stream), "route_sort")
         return [idx, w, counts, offsets, token, wsorted, pos_of]
 
     def _grouped(self, fn, name, A, a_rows, B, offsets, rows, swiglu, scale):
@@ -404,7 +409,7 @@ def _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch=None):
     idx, _, counts, offsets, token, wsorted, pos_of = srt
     if mode == "auto":
         mode = auto_mode(idx.numel(), gate_up.shape[0])  # no device-to-host read
-    if mode == "gemv" and 0 < top_k <= 8 and h.shape[0] > 0:
+    if mode == "gemv" and 0 < top_k <= 8 and idx.numel() >= FUSED_COMBINE_MIN_ROWS:
         # streaming shape: the combine rides in the down projection's epilogue (one launch)
         return ext().expert_ffn_combine(h.contiguous(), token, gate_up, down, offsets, wsorted, pos_of, top_k, scratch)
     y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode, scratch=scratch)
@@ -421,12 +426,17 @@ def experts(h, idx, w, gate_up, down, mode="auto"):
     return _sorted_experts(h, [idx, w] + srt, gate_up, down, idx.shape[1], mode)
 
 
-ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what one block can route and sort
-# Measured on a B200: the one-block route+sort wins while every warp of the block routes at most
-# one token; beyond that the separate routing kernel (a warp per token, many blocks) is faster.
-ROUTE_SORT_MAX_TOKENS = 16
-# Up to this many tokens the router GEMM, the routing and the sort are ONE launch (route_fused).
+ROUTE_SORT_MAX_CHOICES = 8192  # sy_route_sort_max_choices(): what the one-launch route + sort handles
+# Up to this many tokens routing and sort are ONE launch (blocks of sixteen tokens, the last block
+# to finish sorts); beyond it the separate routing kernel and the multi-block sort take over.
+ROUTE_SORT_MAX_TOKENS = 256
+# route_fused (router GEMM inside the routing launch) is used up to this many tokens when asked for.
 ROUTE_FUSED_MAX_TOKENS = 64
+FUSED_ROUTER = os.environ.get("SWITCHYARD_FUSED_ROUTER") == "1"
+# From this many sorted rows the streaming mode folds the combine into the expert launch; below,
+# the separate combine kernel (overlapped by programmatic dependent launch) costs the same or less.
+# Measured on a B200 (OLMoE layer, graph replays): 64 tokens 129.9 against 131.4 us, 8 tokens equal.
+FUSED_COMBINE_MIN_ROWS = 256
 
 
 def fused_routing_applies(n_tokens, n_experts, hidden, top_k):
@@ -434,27 +444,31 @@ def fused_routing_applies(n_tokens, n_experts, hidden, top_k):
             8 <= n_experts <= 128 and n_experts % 8 == 0 and hidden % 32 == 0 and 1 <= top_k <= 8)
 
 
-def route_and_sort(h, router, top_k, norm_topk_prob, bias=None, scratch=None):
+def route_and_sort(h, router, top_k, norm_topk_prob, bias=None, scratch=None, fused=None):
     """Everything before the experts: [idx, w, counts, offsets, token, wsorted, pos_of] for h's
-    tokens. One launch for decode-sized batches (router GEMM included), the library GEMM followed
-    by route (+ sort) otherwise. bias: optional [E] tensor in h's dtype added to the logits."""
+    tokens: the library GEMM for the logits (as in the reference, switchyard/kernels.py:30-32),
+    then routing and sort in one launch for decode-sized batches, in two or three beyond.
+    bias: optional [E] tensor in h's dtype added to the logits. fused=True (default: the
+    SWITCHYARD_FUSED_ROUTER environment switch) computes the logits inside the routing launch
+    where `route_fused` applies."""
     X = ext()
     N, E = h.shape[0], router.shape[0]
-    if fused_routing_applies(N, E, h.shape[1], top_k):
+    if (FUSED_ROUTER if fused is None else fused) and fused_routing_applies(N, E, h.shape[1], top_k):
         return X.route_fused(h.contiguous(), router, top_k, norm_topk_prob, bias, scratch=scratch)
     logits = F.linear(h, router)
     if bias is not None:
         logits = logits + bias
     logits = logits.contiguous()
     if 0 < N <= ROUTE_SORT_MAX_TOKENS and N * top_k <= ROUTE_SORT_MAX_CHOICES and E <= 128:
-        return X.route_sort(logits, top_k, norm_topk_prob)
+        return X.route_sort(logits, top_k, norm_topk_prob, scratch)
     idx, w = X.route(logits, top_k, norm_topk_prob)
     return [idx, w] + X.sort_by_expert(idx, w, E)
 
 
 def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto", scratch=None):
-    """route + experts (switchyard/kernels.py:91-93). Decode-sized batches in the streaming mode
-    are two launches: route_fused, then the expert FFN with the combine in its epilogue."""
+    """route + experts (switchyard/kernels.py:91-93): router GEMM, routing + sort (one launch for
+    decode-sized batches), the expert FFN (one launch), combine (folded into the expert launch
+    for streaming-mode batches from 32 tokens)."""
     srt = route_and_sort(h, router, top_k, norm_topk_prob, scratch=scratch)
     return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
 

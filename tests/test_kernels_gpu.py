@@ -38,6 +38,14 @@ def force_tile(K, tile):
     assert K.ext().lib.sy_force_compute_tile(tile) == 0
 
 
+def layer_logits(K, h, router):
+    """The router logits moe_layer routes on: the library GEMM's, or (SWITCHYARD_FUSED_ROUTER=1) the
+    ones the fused routing launch computes and reports."""
+    if K.FUSED_ROUTER and K.fused_routing_applies(h.shape[0], router.shape[0], h.shape[1], 8):
+        return K.ext().route_fused(h, router, 8, False, logits=True)[7]
+    return torch.nn.functional.linear(h, router)
+
+
 def ulp16(t):
     """Spacing of the 16-bit format at |t| (as float32)."""
     mant = 10 if t.dtype == torch.float16 else 7
@@ -139,12 +147,17 @@ def test_route_fused_is_the_kernel_rule_on_its_own_logits(K, N, E, k, H, dtype):
         assert ((w.cpu().float() - ow.float()).abs() <= ulp16(ow)).all()
         for got, want in zip((counts, offsets, token, wsorted, pos_of), K.ext().sort_by_expert(idx, w, E)):
             assert torch.equal(got, want)
+        # the logits: the float32 dot products rounded to 16 bits (one step of slack for a sum that
+        # lands on a rounding boundary, one more for the bias add); the library GEMM, which may
+        # reduce in lower precision, is only required to be close
+        exact = (h.float() @ router.float().t()).to(dtype)
         lib = torch.nn.functional.linear(h, router)
         if b is not None:
-            lib = lib + b
-        assert ((logits.float() - lib.float()).abs() <= 2 * ulp16(lib) + 2e-5).all()
+            exact, lib = exact + b, lib + b
+        assert ((logits.float() - exact.float()).abs() <= (2 if b is not None else 1) * ulp16(exact) + 2e-5).all()
+        assert ((logits.float() - lib.float()).abs() <= 16 * ulp16(lib) + 1e-3).all()
         if b is None and not norm:
-            probs = torch.softmax(lib.float(), -1).cpu()
+            probs = torch.softmax(exact.float(), -1).cpu()
             ridx = probs.topk(k, -1).indices
             same = (idx.cpu().long().sort(-1).values == ridx.sort(-1).values).all(-1)
             for t in torch.nonzero(~same).flatten().tolist():
@@ -237,11 +250,12 @@ def test_route_sort_in_one_launch_equals_the_two_calls(K, N, E, k, dtype):
     for norm in (False, True):
         idx, w = K.ext().route(logits, k, norm)
         want = [idx, w] + K.ext().sort_by_expert(idx, w, E)
-        got = K.ext().route_sort(logits, k, norm)
-        for a, b in zip(got, want):
-            assert torch.equal(a, b)
+        for _ in range(2):  # several blocks route, the last one sorts; the ticket returns to zero
+            got = K.ext().route_sort(logits, k, norm)
+            for a, b in zip(got, want):
+                assert torch.equal(a, b)
     with pytest.raises(RuntimeError):
-        K.ext().route_sort(cases.route_logits(64, 1025).to(DEV), 8, False)  # more than one block sorts
+        K.ext().route_sort(cases.route_logits(64, 1025).to(DEV), 8, False)  # more choices than one block sorts
 
 
 # ------------------------------------------------------------------------------ combine
@@ -308,7 +322,7 @@ def test_sizes_that_fill_no_tile(K, mode, N):
 def test_empty_experts_and_a_single_token(K):
     h, router, gu, dn = cases.layer_inputs(1)
     out = K.moe_layer(h.to(DEV), router.to(DEV), gu.to(DEV), dn.to(DEV), 8, False)
-    ridx, rw = mo.route_kernel_rule(K.ext().route_fused(h.to(DEV), router.to(DEV), 8, False, logits=True)[7].cpu(), 8, False)
+    ridx, rw = mo.route_kernel_rule(layer_logits(K, h.to(DEV), router.to(DEV)).cpu(), 8, False)
     ridx = ridx.long()
     want = mo.experts_reference(h.float(), ridx, rw.float(), gu.float(), dn.float())
     assert (out.float().cpu() - want).abs().max().item() < 2e-3
@@ -441,8 +455,7 @@ def test_olmoe_decode_layer(K, olmoe, tokens, mode):
     h = synthetic.hidden_states(tokens, "cpu", torch.float16, seed=1)
     rd, gud, dnd = router.to(DEV), gu.to(DEV), dn.to(DEV)
     out = K.moe_layer(h.to(DEV), rd, gud, dnd, 8, False, mode).cpu()
-    # the layer routes these sizes with route_fused: the oracle gets the logits that launch computes
-    logits = K.ext().route_fused(h.to(DEV), rd, 8, False, logits=True)[7].cpu()
+    logits = layer_logits(K, h.to(DEV), rd).cpu()
     idx, w = mo.route_kernel_rule(logits, 8, False)
     want = mo.experts_reference(h.float(), idx.long(), w.float(), gu.float(), dn.float())
     loop16 = mo.experts_reference(h, idx.long(), w, gu, dn)
