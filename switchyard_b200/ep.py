@@ -45,49 +45,53 @@ DEFAULT_MAX_TOKENS = 4096
 
 
 class CudaOps:
-    """This package's kernels as the protocol's operations (switchyard/ep.py:66-95).
+    """This package's kernels as the seven operations the host protocol is written in, plus
+    `route_sort`, which the window engine prefers (switchyard/ep.py:66-95 is the reference's
+    class of the same name and duck type).
     mode: "gemv", "gemm" or "auto". logit_bias: optional [E] tensor added to the router logits
     in their dtype before routing (the benchmarks' synthetic routing skew)."""
 
     def __init__(self, mode="auto", logit_bias=None):
-        from . import kernels
-        self.k, self.mode, self.logit_bias = kernels, mode, logit_bias
+        from . import kernels as lib
+        self.k = lib
+        self.mode = mode
+        self.logit_bias = logit_bias
 
     def _bias(self, like):
         b = self.logit_bias
         return None if b is None else b.to(device=like.device, dtype=like.dtype)
 
-    def route_sort(self, h, router, k, norm):
+    def route_sort(self, hidden, router_weight, top_k, renormalise):
         """route + sort in as few launches as the batch size allows (one for decode sizes)."""
-        return self.k.route_and_sort(h, router, k, norm, bias=self._bias(h))
+        return self.k.route_and_sort(hidden, router_weight, top_k, renormalise, bias=self._bias(hidden))
 
-    def route(self, h, router, k, norm):
+    def route(self, hidden, router_weight, top_k, renormalise):
         if self.logit_bias is None:
-            return self.k.route(h, router, k, norm)
-        logits = torch.nn.functional.linear(h, router) + self._bias(h)
-        return self.k.ext().route(logits.contiguous(), k, norm)
+            return self.k.route(hidden, router_weight, top_k, renormalise)
+        logits = torch.nn.functional.linear(hidden, router_weight) + self._bias(hidden)
+        return self.k.ext().route(logits.contiguous(), top_k, renormalise)
 
-    def sort(self, idx, w, E):
-        return self.k.ext().sort_by_expert(idx, w, E)
+    def sort(self, choices, weights, n_experts):
+        return self.k.ext().sort_by_expert(choices, weights, n_experts)
 
-    def ffn(self, x, a_rows, offsets, counts, wsorted, gate_up, down, rows, host_counts=None):
+    def ffn(self, rows_in, picks, offsets, counts, row_weights, gate_up, down, n_rows, host_counts=None):
         mode = self.mode
-        if mode == "auto":
-            biggest = max(host_counts if host_counts is not None else counts.tolist(), default=0)
-            mode = self.k.pick(biggest)
-        return self.k.ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_counts)
+        if mode == "auto":  # per call, from the largest expert's rows (a host list if the caller has one)
+            per_expert = host_counts if host_counts is not None else counts.tolist()
+            mode = self.k.pick(max(per_expert, default=0))
+        return self.k.ffn(rows_in, picks, offsets, counts, row_weights, gate_up, down, n_rows, mode, host_counts)
 
-    def combine(self, y, pos_of, idx, N):
-        return self.k.ext().combine(y, pos_of, idx, N)
+    def combine(self, results, row_of_choice, choices, n_tokens):
+        return self.k.ext().combine(results, row_of_choice, choices, n_tokens)
 
-    def gather_to(self, src, index, dst):
-        self.k.ext().gather_rows(src, index, dst)
+    def gather_to(self, source, rows, destination):
+        self.k.ext().gather_rows(source, rows, destination)
 
-    def copy_to(self, dst, src):
-        self.k.ext().copy_async(dst, src)
+    def copy_to(self, destination, source):
+        self.k.ext().copy_async(destination, source)
 
-    def host(self, t):
-        return t.tolist()
+    def host(self, tensor):
+        return tensor.tolist()
 
 
 class _Scope:
@@ -112,14 +116,14 @@ class ExpertParallel:
     share a device, which exercises the protocol on one GPU)."""
 
     def __init__(self, devices, num_experts, top_k, norm_topk_prob, ops=None):
-        self.devices = [torch.device(d) for d in devices]
-        self.R = len(self.devices)
-        assert num_experts % self.R == 0, "experts must split evenly over the ranks"
-        self.E, self.per = num_experts, num_experts // self.R
-        self.k, self.norm = top_k, norm_topk_prob
-        self.cuda = self.devices[0].type == "cuda"
+        self.devices = list(map(torch.device, devices))
+        self.R, self.E, self.k, self.norm = len(self.devices), num_experts, top_k, norm_topk_prob
+        if self.E % self.R:
+            raise AssertionError(f"{self.E} experts do not split evenly over {self.R} ranks")
+        self.per = self.E // self.R
+        self.cuda = all(d.type == "cuda" for d in self.devices)
         if ops is None:
-            if not self.cuda:
+            if self.devices[0].type != "cuda":
                 raise RuntimeError("switchyard_b200 has no CPU implementation of the MoE operations: "
                                    "use CUDA devices, or pass an `ops` object (tests do)")
             ops = CudaOps()
@@ -132,7 +136,7 @@ class ExpertParallel:
             ids = [d.index if d.index is not None else torch.cuda.current_device() for d in self.devices]
             self.devices = [torch.device("cuda", i) for i in ids]
             self.shared_gpu = len(set(ids)) < self.R
-            self.streams = [torch.cuda.Stream(d) for d in self.devices]
+            self.streams = [torch.cuda.Stream(device=d) for d in self.devices]
             self.mail = [[self.streams[d] for d in range(self.R)] for _ in range(self.R)]  # the reference's name; no own streams here
             uniq = sorted(set(ids))
             self.peer = all(kernels.ext().enable_peer_access(a, b) for a in uniq for b in uniq if a != b)
@@ -152,14 +156,13 @@ class ExpertParallel:
         # capacity_factor: None routes every (token, expert) choice. A number c gives every
         # expert room for ceil(c * rows / E) rows of each rank's batch; later rows of an expert
         # (token order) get weight 0 (switchyard/ep.py:127-132).
-        self.capacity_factor = None
         # trace: None, or a list that receives (rank, per-expert counts) per layer and rank.
-        self.trace = None
-        self._pool = None
-        self.barrier = threading.Barrier(self.R)
+        self.capacity_factor, self.trace = None, None
+        self.barrier, self._pool = threading.Barrier(self.R), None
 
     def owner(self, expert):
-        return expert // self.per
+        """The rank that holds `expert` (contiguous split)."""
+        return int(expert) // self.per
 
     # ------------------------------------------------------------------ bookkeeping
     @property
@@ -196,8 +199,9 @@ class ExpertParallel:
     def new_state(self):
         """A layer's shared state: what each rank keeps (`st`), what it was sent (`inbox[d][r]`,
         host protocol only) and the events that order the phases (`back`)."""
-        R = self.R
-        return dict(st=[None] * R, inbox=[[None] * R for _ in range(R)], back=[[None] * 3 for _ in range(R)])
+        ranks = range(self.R)
+        return {"st": [None for _ in ranks], "inbox": [[None for _ in ranks] for _ in ranks],
+                "back": [[None, None, None] for _ in ranks]}
 
     def _rank(self, r):
         if not self.cuda:
@@ -269,16 +273,16 @@ class ExpertParallel:
         sorted rows (with their router weights and the run's per-expert offsets)."""
         # The layer may not read h before the caller's stream has produced it: take the caller's
         # stream before the rank's own stream becomes current (switchyard/ep.py:177-183).
-        caller = torch.cuda.current_stream(self.devices[r]) if self.cuda else None
+        callers_stream = torch.cuda.current_stream(self.devices[r]) if self.cuda else None
         with self._rank(r):
-            if caller is not None:
-                self.streams[r].wait_stream(caller)
+            if self.cuda:
+                self.streams[r].wait_stream(callers_stream)
             srt = self._route_sort(h, router)
             idx, counts, offsets, wsorted = srt[0], srt[2], srt[3], srt[5]
             if self.capacity_factor is not None:
                 wsorted = self._drop(r, offsets, counts, wsorted)
-            if self.trace is not None:
-                self.trace.append((r, counts.clone()))
+            if isinstance(self.trace, list):
+                self.trace.append((r, counts.detach().clone()))
             keep = dict(idx=idx, counts=counts, offsets=offsets, token=srt[4], wsorted=wsorted, pos_of=srt[6], h=h)
             sh["st"][r] = keep
             if self.windows:
@@ -291,14 +295,14 @@ class ExpertParallel:
         ops = self.ops
         if self.windows and hasattr(ops, "route_sort"):
             return ops.route_sort(h, router, self.k, self.norm)
-        idx, w = ops.route(h, router, self.k, self.norm)
-        return [idx, w] + list(ops.sort(idx, w, self.E))
+        choices, weights = ops.route(h, router, self.k, self.norm)
+        return [choices, weights, *ops.sort(choices, weights, self.E)]
 
     def _drop(self, r, offsets, counts, wsorted):
         """Weight 0 for the rows past each expert's capacity, ceil(c * rows / E) rows per expert
         in sorted (= token) order (switchyard/ep.py:226-237). Nothing is read back here."""
-        M = wsorted.shape[0]
-        if M == 0:
+        M = wsorted.numel()
+        if not M:
             return wsorted
         room = math.ceil(self.capacity_factor * M / self.E)
         first = torch.repeat_interleave(offsets[:-1].long(), counts.long(), output_size=M)
@@ -421,46 +425,44 @@ class ExpertParallel:
         rank's tokens. All ranks driven from this thread (switchyard/ep.py:274-285)."""
         if self.windows:
             self.reserve(max(h.shape[0] for h in hs))
-        sh = self.new_state()
-        for r in range(self.R):
-            self.phase_send(sh, r, hs[r], routers[r])
-        for d in range(self.R):
-            self.phase_compute(sh, d, hs[d], gate_ups[d], downs[d])
-        outs = [self.phase_combine(sh, r, hs[r].shape[0]) for r in range(self.R)]
-        self._keep = sh  # what the enqueued kernels read stays referenced until the next layer
-        return outs
+        state = self.new_state()
+        for r, (h, router) in enumerate(zip(hs, routers)):
+            self.phase_send(state, r, h, router)
+        for r, (h, gate_up, down) in enumerate(zip(hs, gate_ups, downs)):
+            self.phase_compute(state, r, h, gate_up, down)
+        results = [self.phase_combine(state, r, h.shape[0]) for r, h in enumerate(hs)]
+        self._keep = state  # what the enqueued kernels read stays referenced until the next layer
+        return results
 
     def layer_rank(self, sh, r, h, router, gate_up, down):
         """Rank r's part of one layer, from rank r's thread (switchyard/ep.py:289-296). Ranks whose
         phases are ordered on the host meet at the barrier between phases; ranks on distinct GPUs
         over windows do not meet at all: their kernels wait for each other's flags."""
+        meet = self.barrier.wait if self.host_ordered else (lambda: None)
         self.phase_send(sh, r, h, router)
-        if self.host_ordered:
-            self.barrier.wait()
+        meet()
         self.phase_compute(sh, r, h, gate_up, down)
-        if self.host_ordered:
-            self.barrier.wait()
-        return self.phase_combine(sh, r, h.shape[0])
+        meet()
+        return self.phase_combine(sh, r, len(h))
 
     def run_ranks(self, fn):
         """fn(r) in one thread per rank (a persistent pool); results in rank order. A rank that
         raises breaks the barrier so that the others stop instead of waiting for it, and its
         exception (not their BrokenBarrierError) is what the caller sees (switchyard/ep.py:298-321)."""
-        if self._pool is None:
-            self._pool = ThreadPoolExecutor(self.R, thread_name_prefix="switchyard-rank")
+        self._pool = self._pool or ThreadPoolExecutor(max_workers=self.R, thread_name_prefix="sy-rank")
 
-        def one(r):
+        def one(rank):
+            if self.cuda:
+                torch.cuda.set_device(self.devices[rank])
             try:
-                if self.cuda:
-                    torch.cuda.set_device(self.devices[r])
-                return fn(r)
+                return fn(rank)
             except BaseException:
-                self.barrier.abort()
+                self.barrier.abort()  # the others must not wait for a rank that is gone
                 raise
 
-        jobs = [self._pool.submit(one, r) for r in range(self.R)]
+        jobs = [self._pool.submit(one, rank) for rank in range(self.R)]
         failures = [j.exception() for j in jobs]  # returns once every rank has finished
-        if self.barrier.broken:
+        if self.barrier.broken:  # usable again for the next call
             self.barrier.reset()
         own = [f for f in failures if f is not None and not isinstance(f, threading.BrokenBarrierError)]
         if own:
@@ -473,10 +475,14 @@ class ExpertParallel:
         """Same as layer(), every rank driven by its own thread."""
         if self.windows:
             self.reserve(max(h.shape[0] for h in hs))
-        sh = self.new_state()
-        outs = self.run_ranks(lambda r: self.layer_rank(sh, r, hs[r], routers[r], gate_ups[r], downs[r]))
-        self._keep = sh
-        return outs
+        state = self.new_state()
+
+        def rank_part(r):
+            return self.layer_rank(state, r, hs[r], routers[r], gate_ups[r], downs[r])
+
+        results = self.run_ranks(rank_part)
+        self._keep = state
+        return results
 
     def check(self):
         """Raises RuntimeError if a kernel of any rank gave up on a bounded wait (a peer that never
