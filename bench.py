@@ -340,8 +340,8 @@ def run_single_gpu(args):
     e2e_ms = e0.elapsed_time(e1)
     io_bytes = sum(T * H * 2 for T in SWEEP)
 
-    # ---- the dominant kernel alone: the fused expert launch of T=64 (both weight streams and the
-    # combine in its epilogue: the launch the layer runs), one launch per weight set in rotation
+    # ---- the dominant kernel alone: the fused expert launch of T=64 (both weight streams: the
+    # launch the layer runs), one launch per weight set in rotation
     T = SWEEP[-1]
     ext = kernels.ext()
     kern_ms, kern_bytes = [], []
@@ -357,7 +357,7 @@ def run_single_gpu(args):
             a.record(stream)
             for l in range(LAYERS):
                 token, offsets, wsorted, pos_of = sorted_in[l]
-                ext.expert_ffn_combine(hs[T], token, layers[l][1], layers[l][2], offsets, wsorted, pos_of, TOPK)
+                ext.expert_ffn(hs[T], token, layers[l][1], layers[l][2], offsets, T * TOPK, wsorted, 0)
             b.record(stream)
             stream.synchronize()
             if rep >= 2:
@@ -383,7 +383,7 @@ def run_single_gpu(args):
         "dtype": "f16", "data": "synthetic",
         "config": CONFIG,
         "arm": {"mode": mode, "path": "router GEMM (library) -> route + sort (one launch) -> expert FFN (tcgen05 weight "
-                                      "stream, one launch; from 32 tokens with the combine in its epilogue) -> combine",
+                                      "stream, both projections in one launch) -> combine",
                 "timing": "CUDA events on the launch stream around K replays of CUDA graphs holding one step "
                           "(the four layer passes back to back); `sweep` times each pass's own graph separately"},
         "sweep": sweep,
@@ -397,7 +397,7 @@ def run_single_gpu(args):
         "gpu_launches": args.steps * sum(2 + (T * TOPK < kernels.FUSED_COMBINE_MIN_ROWS) for T in SWEEP),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "traffic_source": traffic_src, "peak_source": peak_src,
-                     "kernel": "gemm_umma_kernel<half, streaming shape>: gate/up + down projections + combine (sy_expert_ffn_combine)",
+                     "kernel": "gemm_umma_kernel<half, streaming shape>: gate/up + down projections (sy_expert_ffn)",
                      "workload": "T=64, one layer's experts in one launch, weight sets in rotation",
                      "bytes_per_launch": statistics.mean(kern_bytes), "us_per_launch": statistics.mean(kern_ms) * 1e3,
                      "vs_nominal_8TBps": achieved / 8000.0},

@@ -258,8 +258,8 @@ int sy_grouped_segments(const void* A, const void* B, const int32_t* begins, con
  * switchyard/ep.py:193-223): row i (expert in [d*experts_per_rank, (d+1)*experts_per_rank)) is
  * copied from h[token[i]] to row i - offsets[d*experts_per_rank] of x_dst[d], its router weight
  * to w_dst[d]; meta_dst[d] gets experts_per_rank+1 rebased offsets, the segment's first row and
- * its row count. As soon as everything bound for receiver d is stored, *flag_dst[d] becomes
- * *epoch_counter + 1 (release, system scope); the last block out then advances *epoch_counter.
+ * its row count. When everything is stored, *flag_dst[d] becomes *epoch_counter + 1 (release,
+ * system scope) for every d and *epoch_counter advances.
  * rows_bound: the number of sorted rows as the host knows it (sizes the grid; the kernel takes
  * the exact count from offsets; 0 still publishes empty mailboxes). counters:
  * sy_ep_dispatch_scratch_bytes(n_ranks) bytes of this rank's memory, zero before the first call,
@@ -273,17 +273,27 @@ int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, con
 
 /* ep_expert_ffn — sy_expert_ffn over this rank's mailbox (replaces switchyard/ep.py:239-262: one
  * ffn per received segment, a copy back and an event each). The kernel waits (bounded) until
- * arrive_flags[s] >= *epoch_counter for every sender s, builds its row ranges from the senders'
- * metadata (range e*n_ranks + s = sender s's rows of local expert e; sender s's rows start at
- * s*capacity of x_mail / w_mail; an expert's ranges share its tiles, so its weights are read
- * once), and the down projection's epilogue stores result row i of sender s's segment into
+ * arrive_flags[s] has reached the layer's epoch for every sender s, builds its row ranges from the
+ * senders' metadata (range e*n_ranks + s = sender s's rows of local expert e; sender s's rows
+ * start at s*capacity of x_mail / w_mail; an expert's ranges share its tiles, so its weights are
+ * read once), and the down projection's epilogue stores result row i of sender s's segment into
  * y_dst[s] + (first row of the segment in the sender's sort + i) * hidden * 2 bytes. When the
- * whole launch is done, *ret_flag_dst[s] = *epoch_counter (release, system scope) for every s.
+ * whole launch is done, *ret_flag_dst[s] = epoch (release, system scope) for every s.
+ * With push_counter != NULL the launch also does the layer's dispatch in its prologue, which
+ * takes sy_ep_dispatch off the critical path: the push_* arguments, self_rank, x_dst .. flag_dst,
+ * push_counter and stats are sy_ep_dispatch's h, token, wsorted, offsets, rows_bound, self_rank,
+ * x_dst .. flag_dst, counters and stats; the layer's epoch is then *epoch_counter + 1 and the
+ * launch advances *epoch_counter when it ends. With push_counter == NULL a sy_ep_dispatch before
+ * it has done both (the form for ranks that share one GPU and order their steps by events).
  * act: 16-bit [n_ranks*capacity, inter] scratch. scratch: as sy_expert_ffn. */
 int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const int32_t* meta, const int32_t* arrive_flags,
-                     const int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity, const void* gate_up,
+                     int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity, const void* gate_up,
                      const void* down, int hidden, int inter, void* act, void* const* y_dst,
-                     int32_t* const* ret_flag_dst, int32_t* scratch, int dtype, int compute_shape, void* stream);
+                     int32_t* const* ret_flag_dst, int32_t* scratch, int dtype, int compute_shape, const void* push_h,
+                     const int32_t* push_token, const void* push_wsorted, const int32_t* push_offsets,
+                     int push_rows_bound, int self_rank, void* const* x_dst, void* const* w_dst,
+                     int32_t* const* meta_dst, int32_t* const* flag_dst, int32_t* push_counter, int64_t* stats,
+                     void* stream);
 
 /* ep_wait — one small kernel that waits (bounded, see sy_set_wait_limit_ns) until
  * flags[i] >= *epoch_counter + epoch_offset for i < n (n <= 32). The building block of the waits

@@ -149,7 +149,14 @@ class _Lib:
                     out[r] = acc.to(dt)[0]
 
     def sy_ep_expert_ffn(self, x_mail, w_mail, meta, arrive_flags, epoch_counter, R, per, cap, gate_up, down, hidden,
-                         inter, act, y_dst, ret_flag_dst, scratch, dtype, compute_shape, stream):
+                         inter, act, y_dst, ret_flag_dst, scratch, dtype, compute_shape, push_h, push_token, push_wsorted,
+                         push_offsets, push_rows, self_rank, x_dst, w_dst, meta_dst, flag_dst, push_counter, stats, stream):
+        if _addr(push_counter):  # the dispatch in the same "launch"
+            rc = self.sy_ep_dispatch(push_h, push_token, push_wsorted, push_offsets, push_rows, per, R, self_rank,
+                                     hidden * 2, cap, x_dst, w_dst, meta_dst, flag_dst, push_counter, epoch_counter, stats,
+                                     stream)
+            if rc:
+                return rc
         epoch = int(_view(epoch_counter, 1, np.int32)[0])
         if not self._wait(arrive_flags, R, epoch):
             return -3

@@ -6,22 +6,23 @@
 // offsets), flags, and the buffer `y` that its own combine reads. One layer, per rank, on the
 // rank's stream:
 //
-//   dispatch    (sy_ep_dispatch) every sorted row goes to the rank that owns its expert, written
+//   dispatch    (csrc/ep_push.cuh) every sorted row goes to the rank that owns its expert, written
 //               straight into that rank's mailbox over NVLink (the rank's own rows too, locally),
 //               together with the rebased per-expert offsets, the segment's first row and its row
-//               count. Blocks count the rows they have stored per destination; the block that
-//               completes a destination release-stores the layer's epoch into that receiver's
-//               arrival flag at once, so a receiver never waits for rows bound elsewhere;
+//               count; the block that stores last release-stores the layer's epoch into every
+//               receiver's arrival flag. It runs in the prologue of the expert kernel (one launch
+//               less on the critical path), or as a launch of its own (sy_ep_dispatch) for callers
+//               that must order the steps themselves;
 //   experts     (sy_ep_expert_ffn, csrc/gemm.cu) the fused expert kernel waits for all senders'
 //               arrival flags itself, builds its row ranges from the mailboxes' offsets in shared
 //               memory, and its down-projection epilogue stores each result row into the SENDER's
 //               `y` at the row the sender's own sort gave it: the return trip is part of the
-//               epilogue. The block that stores the last result tile release-stores the epoch
-//               into every sender's return flag;
+//               epilogue. The last block out release-stores the epoch into every sender's return
+//               flag;
 //   combine     (sy_ep_combine) waits for every owner's return flag, then sums each token's rows.
 //
-// Flags only ever grow: the epoch is a per-rank layer counter kept in device memory (the
-// dispatch's last block advances it, the later kernels of the layer read it), so nothing is
+// Flags only ever grow: the epoch is a per-rank layer counter kept in device memory (advanced
+// when the dispatch is complete, read by the layer's later kernels), so nothing is
 // reset between layers, the host passes no per-layer value, and a layer can be captured in a
 // CUDA graph and replayed. All ranks run the same sequence of layers, so their counters agree.
 // A mailbox is overwritten by layer n+1's dispatch only after its sender has passed layer n's
@@ -38,97 +39,25 @@
 #include <string.h>
 
 #include "combine.cuh"
+#include "ep_push.cuh"
 
 namespace sy {
 
-constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_THREADS = 256;
 
-struct DispatchTargets {
-  unsigned char* x[EP_MAX_RANKS];   // receiver d's mailbox rows for this sender
-  unsigned char* w[EP_MAX_RANKS];   // ... router weights
-  int* meta[EP_MAX_RANKS];          // ... [per+1 rebased offsets | first row | row count]
-  int* flag[EP_MAX_RANKS];          // ... arrival flag of this sender
-};
-
-// counters: [R] units stored per destination (a row counts one, the metadata one), [1] blocks
-// that have finished; all zero between launches. stats: [0] rows sent to other ranks, [1] rows
-// kept, accumulated over the layers (read by the host when it wants them).
+// The dispatch as a launch of its own (the expert kernel can also do it in its prologue, see
+// sy_ep_expert_ffn): push, and the block that completes it advances the epoch that the layer's
+// later kernels read.
 __global__ void __launch_bounds__(EP_THREADS)
-ep_dispatch_kernel(const uint4* __restrict__ h, const int* __restrict__ token, const unsigned short* __restrict__ wsorted,
-                   const int* __restrict__ offsets, int per, int R, int self, int vec_per_row, int cap, DispatchTargets tg,
-                   int* counters, int* epoch_counter, long long* stats, int* status) {
+ep_dispatch_kernel(PushArgs p, int* epoch_counter, int* status) {
   __shared__ int s_seg[EP_MAX_RANKS + 1];
+  __shared__ int s_done;
   pdl_launch_dependents();
   pdl_wait();  // offsets, token, wsorted come from the sort before this kernel
-  if ((int)threadIdx.x <= R) s_seg[threadIdx.x] = offsets[threadIdx.x * per];
-  __syncthreads();
-  const int epoch = *epoch_counter + 1;  // advanced by the last block out, after every block has read it
-  const int rows = s_seg[R];
-
-  // One more unit of destination d is in place: n rows (or the metadata). The caller's stores
-  // come first (block barrier), then a system-scope fence, then the count; whoever completes
-  // the destination publishes it.
-  auto stored = [&](int d, int n) {
-    __syncthreads();
-    if (threadIdx.x == 0 && n > 0) {
-      __threadfence_system();
-      const int target = s_seg[d + 1] - s_seg[d] + 1;
-      if (atomicAdd(counters + d, n) + n == target) st_release_sys(tg.flag[d], epoch);
-    }
-  };
-
-  if (blockIdx.x == 0) {
-    const int meta_ints = per + 3;
-    for (int t = threadIdx.x; t < R * meta_ints; t += EP_THREADS) {
-      const int d = t / meta_ints, j = t - d * meta_ints;
-      int v;
-      if (j <= per) v = offsets[d * per + j] - s_seg[d];
-      else if (j == per + 1) v = s_seg[d];
-      else v = min(s_seg[d + 1] - s_seg[d], cap);
-      tg.meta[d][j] = v;
-    }
-    __syncthreads();
-    if ((int)threadIdx.x < R) {  // one thread per destination: fence, count the metadata, maybe publish
-      __threadfence_system();
-      const int d = threadIdx.x, target = s_seg[d + 1] - s_seg[d] + 1;
-      if (atomicAdd(counters + d, 1) + 1 == target) st_release_sys(tg.flag[d], epoch);
-    }
-    if (threadIdx.x == 0 && stats) {
-      const int kept = s_seg[self + 1] - s_seg[self];
-      stats[0] += rows - kept;
-      stats[1] += kept;
-    }
-  }
-  int cur = -1, n_cur = 0, d = 0;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    while (d + 1 < R && s_seg[d + 1] <= row) ++d;
-    if (d != cur) {
-      if (cur >= 0) stored(cur, n_cur);
-      cur = d;
-      n_cur = 0;
-    }
-    ++n_cur;
-    const int r = row - s_seg[d];
-    if (r >= cap) {  // cannot happen when the caller respects its capacity; never write past a mailbox
-      if (threadIdx.x == 0) *status = DS_BAD_INDEX;
-      continue;
-    }
-    const uint4* src = h + (size_t)token[row] * vec_per_row;
-    uint4* dst = reinterpret_cast<uint4*>(tg.x[d]) + (size_t)r * vec_per_row;
-    for (int i = threadIdx.x; i < vec_per_row; i += EP_THREADS) dst[i] = __ldg(src + i);
-    if (threadIdx.x == 0) reinterpret_cast<unsigned short*>(tg.w[d])[r] = wsorted[row];
-  }
-  if (cur >= 0) stored(cur, n_cur);
-  // the last block out advances the epoch and leaves the counters at zero for the next layer
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  const int epoch = *epoch_counter + 1;  // advanced below, once everything is stored
+  if (push_rows(p, epoch, status, s_seg, &s_done) && threadIdx.x == 0) {
+    *epoch_counter = epoch;
     __threadfence();
-    if (atomicAdd(counters + R, 1) == (int)gridDim.x - 1) {
-      for (int i = 0; i <= R; ++i) counters[i] = 0;
-      *epoch_counter = epoch;  // read by the layer's later kernels, which follow in stream order
-      __threadfence();
-    }
   }
 }
 
@@ -159,7 +88,45 @@ ep_combine_kernel(const int* ret_flags, int R, const int* epoch_counter, const T
 
 }  // namespace sy
 
-extern "C" size_t sy_ep_dispatch_scratch_bytes(int n_ranks) { return sizeof(int32_t) * (size_t)(n_ranks + 1); }
+namespace sy {
+// Fills and checks the dispatch arguments shared by sy_ep_dispatch and sy_ep_expert_ffn.
+int make_push_args(PushArgs* out, const char* name, const void* h, const int32_t* token, const void* wsorted,
+                   const int32_t* offsets, int rows_bound, int experts_per_rank, int n_ranks, int self_rank,
+                   int row_bytes, int capacity, void* const* x_dst, void* const* w_dst, int32_t* const* meta_dst,
+                   int32_t* const* flag_dst, int32_t* counter, int64_t* stats) {
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS, "%s: 1..%d ranks (got %d)", name, EP_MAX_RANKS, n_ranks);
+  SY_REQUIRE(self_rank >= 0 && self_rank < n_ranks, "%s: rank %d of %d", name, self_rank, n_ranks);
+  SY_REQUIRE(rows_bound >= 0 && experts_per_rank >= 1 && capacity >= 1, "%s: bad sizes", name);
+  SY_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "%s: row size must be a multiple of 16 bytes", name);
+  SY_REQUIRE(offsets && x_dst && w_dst && meta_dst && flag_dst && counter, "%s: null pointer", name);
+  SY_REQUIRE(rows_bound == 0 || (h && token && wsorted), "%s: null pointer", name);
+  PushArgs p;
+  memset(&p, 0, sizeof(p));
+  p.h = static_cast<const uint4*>(h);
+  p.token = token;
+  p.wsorted = static_cast<const unsigned short*>(wsorted);
+  p.offsets = offsets;
+  p.per = experts_per_rank;
+  p.R = n_ranks;
+  p.self = self_rank;
+  p.vec_per_row = row_bytes / 16;
+  p.cap = capacity;
+  for (int d = 0; d < n_ranks; ++d) {
+    p.x[d] = static_cast<unsigned char*>(x_dst[d]);
+    p.w[d] = static_cast<unsigned char*>(w_dst[d]);
+    p.meta[d] = meta_dst[d];
+    p.flag[d] = flag_dst[d];
+    SY_REQUIRE(p.x[d] && p.w[d] && p.meta[d] && p.flag[d] && (uintptr_t)p.x[d] % 16 == 0, "%s: bad target for rank %d",
+               name, d);
+  }
+  p.counter = counter;
+  p.stats = reinterpret_cast<long long*>(stats);
+  *out = p;
+  return SY_OK;
+}
+}  // namespace sy
+
+extern "C" size_t sy_ep_dispatch_scratch_bytes(int n_ranks) { return sizeof(int32_t); }
 
 extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, const int32_t* offsets,
                               int rows_bound, int experts_per_rank, int n_ranks, int self_rank, int row_bytes,
@@ -167,23 +134,13 @@ extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* w
                               int32_t* const* flag_dst, int32_t* counters, int32_t* epoch_counter, int64_t* stats,
                               void* stream) {
   using namespace sy;
-  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS, "ep_dispatch: 1..%d ranks (got %d)", EP_MAX_RANKS, n_ranks);
-  SY_REQUIRE(self_rank >= 0 && self_rank < n_ranks, "ep_dispatch: rank %d of %d", self_rank, n_ranks);
-  SY_REQUIRE(rows_bound >= 0 && experts_per_rank >= 1 && capacity >= 1, "ep_dispatch: bad sizes");
-  SY_REQUIRE(row_bytes > 0 && row_bytes % 16 == 0, "ep_dispatch: row size must be a multiple of 16 bytes");
-  SY_REQUIRE(offsets && x_dst && w_dst && meta_dst && flag_dst && counters && epoch_counter, "ep_dispatch: null pointer");
-  SY_REQUIRE(rows_bound == 0 || (h && token && wsorted), "ep_dispatch: null pointer");
-  DispatchTargets tg;
-  for (int d = 0; d < n_ranks; ++d) {
-    tg.x[d] = static_cast<unsigned char*>(x_dst[d]);
-    tg.w[d] = static_cast<unsigned char*>(w_dst[d]);
-    tg.meta[d] = meta_dst[d];
-    tg.flag[d] = flag_dst[d];
-    SY_REQUIRE(tg.x[d] && tg.w[d] && tg.meta[d] && tg.flag[d] && (uintptr_t)tg.x[d] % 16 == 0,
-               "ep_dispatch: bad target for rank %d", d);
-  }
+  SY_REQUIRE(epoch_counter, "ep_dispatch: null pointer");
+  PushArgs p;
+  int rc = make_push_args(&p, "ep_dispatch", h, token, wsorted, offsets, rows_bound, experts_per_rank, n_ranks, self_rank,
+                          row_bytes, capacity, x_dst, w_dst, meta_dst, flag_dst, counters, stats);
+  if (rc != SY_OK) return rc;
   int sms = 0;
-  int rc = device_sm_count(&sms);
+  rc = device_sm_count(&sms);
   if (rc != SY_OK) return rc;
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
@@ -191,9 +148,7 @@ extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* w
   // takes the real row count from offsets
   const int blocks = rows_bound < 1 ? 1 : (rows_bound < sms * 4 ? rows_bound : sms * 4);
   return launch_kernel(ep_dispatch_kernel, blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream), "ep_dispatch launch",
-                       static_cast<const uint4*>(h), token, static_cast<const unsigned short*>(wsorted), offsets,
-                       experts_per_rank, n_ranks, self_rank, row_bytes / 16, capacity, tg, counters, epoch_counter,
-                       reinterpret_cast<long long*>(stats), status);
+                       p, epoch_counter, status);
 }
 
 extern "C" int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, int epoch_offset, void* stream) {

@@ -43,6 +43,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "ep_push.cuh"
 
 namespace sy {
 
@@ -61,7 +62,7 @@ constexpr int GM_MAX_BN = 256;                      // most token rows in a tile
 constexpr int GM_EPI_ROWS = 64;                    // token rows the epilogue stages per pass
 constexpr int GM_EPI_BYTES = GM_EPI_ROWS * GM_BM * 2;  // staged output tile: 64 rows x 128 columns
 constexpr int GM_SMEM = GM_RING_BYTES + GM_EPI_BYTES + 1024;  // + room to align the ring to 1024
-constexpr int GM_MAX_RANKS = 16;                   // ranks of an expert-parallel group
+constexpr int GM_MAX_RANKS = EP_MAX_RANKS;          // ranks of an expert-parallel group
 constexpr int COMBINE_K = 8;                       // most choices per token the fused combine handles
 
 // Three shapes of the same kernel.
@@ -124,14 +125,17 @@ struct Problem {
 // builds the row ranges (range e * R + s = sender s's rows of local expert e) and the table of
 // where each range's results go (into the SENDER's result buffer, at the rows its own sort gave
 // them), and when its last result tile has been stored it release-stores the layer's epoch into
-// every sender's return flag.
+// every sender's return flag. With push.counter set the kernel first does the layer's dispatch
+// itself (csrc/ep_push.cuh: this rank's rows into the owners' mailboxes, their arrival flags) and
+// advances the epoch when it ends; otherwise a dispatch launch has done both before it.
 struct EpArgs {
   const int* arrive;
   const int* meta;
-  const int* epoch_counter;
+  int* epoch_counter;
   int R, per, cap, out_row_bytes;
   unsigned char* y[GM_MAX_RANKS];
   int* ret_flag[GM_MAX_RANKS];
+  PushArgs push;
 };
 
 // Combine fused into the last problem's epilogue (streaming shape, local results): every result
@@ -525,6 +529,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ float s_xch[2][GM_BM / 2][9];  // up-projection values handed to the gate warps (one-accumulator SwiGLU)
   __shared__ unsigned long long s_ctab[GM_MAX_E];  // per-range output row pointers (given, or built in expert-parallel mode)
   __shared__ int s_flag_ok;
+  __shared__ int s_epoch;
+  __shared__ int s_push_seg[GM_MAX_RANKS + 1];
+  __shared__ int s_push_done;
   __shared__ int s_final[GM_MAX_BN];       // fused combine: tokens this tile completes
   __shared__ int s_nfinal;
 
@@ -585,9 +592,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   if (args.ep.arrive) {
     // expert-parallel: wait for every sender's rows, then build the ranges and the result table
     const int R = args.ep.R, per = args.ep.per, cap = args.ep.cap;
-    if (threadIdx.x == 0) s_flag_ok = 1;
+    const bool pushes = args.ep.push.counter != nullptr;
+    const int epoch = *args.ep.epoch_counter + (pushes ? 1 : 0);
+    if (threadIdx.x == 0) {
+      s_flag_ok = 1;
+      s_epoch = epoch;
+    }
+    if (pushes) push_rows(args.ep.push, epoch, status, s_push_seg, &s_push_done);  // the layer's dispatch, in this launch
     __syncthreads();
-    const int epoch = *args.ep.epoch_counter;
     if ((int)threadIdx.x < R && !wait_flag(args.ep.arrive + threadIdx.x, epoch, GM_WAIT_NS)) {
       *status = DS_TIMEOUT_FLAG;
       s_flag_ok = 0;
@@ -987,8 +999,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       for (int e = 0; e <= EL; ++e) args.ready[e] = 0;
       if (args.ep.arrive) {
         __threadfence_system();
-        const int epoch = *args.ep.epoch_counter;
+        const int epoch = s_epoch;
         for (int r = 0; r < args.ep.R; ++r) st_release_sys(args.ep.ret_flag[r], epoch);
+        if (args.ep.push.counter) *args.ep.epoch_counter = epoch;  // the combine that follows reads it
+        __threadfence();
       } else {
         __threadfence();
       }
@@ -1341,11 +1355,21 @@ extern "C" int sy_expert_ffn_combine(const void* x, const int32_t* token, const 
   return grouped_umma(false, "expert_ffn_combine", a, rows);
 }
 
+namespace sy {
+int make_push_args(PushArgs* out, const char* name, const void* h, const int32_t* token, const void* wsorted,
+                   const int32_t* offsets, int rows_bound, int experts_per_rank, int n_ranks, int self_rank,
+                   int row_bytes, int capacity, void* const* x_dst, void* const* w_dst, int32_t* const* meta_dst,
+                   int32_t* const* flag_dst, int32_t* counter, int64_t* stats);
+}
+
 extern "C" int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const int32_t* meta, const int32_t* arrive_flags,
-                                const int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity,
+                                int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity,
                                 const void* gate_up, const void* down, int hidden, int inter, void* act,
                                 void* const* y_dst, int32_t* const* ret_flag_dst, int32_t* scratch, int dtype,
-                                int compute_shape, void* stream) {
+                                int compute_shape, const void* push_h, const int32_t* push_token,
+                                const void* push_wsorted, const int32_t* push_offsets, int push_rows_bound,
+                                int self_rank, void* const* x_dst, void* const* w_dst, int32_t* const* meta_dst,
+                                int32_t* const* flag_dst, int32_t* push_counter, int64_t* stats, void* stream) {
   using namespace sy;
   SY_REQUIRE(n_ranks >= 1 && n_ranks <= GM_MAX_RANKS && experts_per_rank >= 1 && capacity >= 1,
              "ep_expert_ffn: 1..%d ranks (got %d)", GM_MAX_RANKS, n_ranks);
@@ -1365,6 +1389,12 @@ extern "C" int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const in
     a.ep.y[r] = static_cast<unsigned char*>(y_dst[r]);
     a.ep.ret_flag[r] = ret_flag_dst[r];
     SY_REQUIRE(a.ep.y[r] && a.ep.ret_flag[r] && (uintptr_t)a.ep.y[r] % 16 == 0, "ep_expert_ffn: bad target for rank %d", r);
+  }
+  if (push_counter) {  // the dispatch runs in this launch's prologue
+    int rc = make_push_args(&a.ep.push, "ep_expert_ffn", push_h, push_token, push_wsorted, push_offsets, push_rows_bound,
+                            experts_per_rank, n_ranks, self_rank, hidden * 2, capacity, x_dst, w_dst, meta_dst, flag_dst,
+                            push_counter, stats);
+    if (rc != SY_OK) return rc;
   }
   return grouped_umma(compute_shape != 0, "ep_expert_ffn", a, n_ranks * capacity);
 }

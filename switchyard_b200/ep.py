@@ -13,15 +13,16 @@ switchyard/ep.py:66-343, so the reference's `serve.ParallelModel` and tests driv
 unchanged. How a layer moves is new. There are two engines behind the three phases:
 
   * windows (CUDA ranks with `CudaOps`): every rank owns a window of device memory that all
-    ranks address directly (peer access). A rank's layer is three launches on its own stream and
-    no host read: `sy_ep_dispatch` stores rows, weights and offsets into the owners' mailboxes
-    and raises their arrival flags; `sy_ep_expert_ffn` waits for the flags on the device, runs the
-    experts over the whole mailbox and stores each result row into the sender's `y`, then raises
-    the senders' return flags; `sy_ep_combine` waits for those and sums. Ranks on different GPUs
-    need neither events nor host barriers. Ranks that share a GPU (tests do that) must not wait
+    ranks address directly (peer access). After routing and sort a rank's layer is two launches
+    on its own stream and no host read: `sy_ep_expert_ffn` first stores the rank's rows, weights
+    and offsets into the owners' mailboxes and raises their arrival flags, waits for its own
+    senders' flags on the device, runs the experts over the whole mailbox and stores each result
+    row into the sender's `y`, then raises the senders' return flags; `sy_ep_combine` waits for
+    those and sums. Ranks on different GPUs need neither events nor host barriers. Ranks that share a GPU (tests do that) must not wait
     for each other on the device, so there each phase is followed by an event and preceded by
-    waits for the previous phase's events, and `layer_rank` keeps the reference's barriers; the
-    kernels are the same, their flag waits then find the flags already raised.
+    waits for the previous phase's events, the dispatch is a launch of its own (`sy_ep_dispatch`),
+    and `layer_rank` keeps the reference's barriers; the kernels are the same, their flag waits
+    then find the flags already raised.
     Windows have a fixed capacity (`max_tokens` per rank and layer, default 4096 or
     SWITCHYARD_EP_MAX_TOKENS); `layer()` / `layer_threaded()` grow them on demand, `layer_rank()`
     cannot (a rank does not know its peers' batch sizes) and raises: call `reserve(n)` first.
@@ -324,9 +325,9 @@ class ExpertParallel:
         chan = self._channels(h.shape[1], h.dtype)[r]
         h = h.contiguous()
         keep["h"] = h
-        stream = torch.cuda.current_stream().cuda_stream
-        chan.dispatch(h.data_ptr(), keep["token"].data_ptr(), keep["wsorted"].data_ptr(), keep["offsets"].data_ptr(),
-                      N * self.k, stream)
+        if self.host_ordered:  # ranks share a GPU: the dispatch is a launch of its own, followed by an event
+            chan.dispatch(h.data_ptr(), keep["token"].data_ptr(), keep["wsorted"].data_ptr(), keep["offsets"].data_ptr(),
+                          N * self.k, torch.cuda.current_stream().cuda_stream)
 
     def _send_ops(self, sh, r, h, keep):
         """Host protocol: one read of the offsets, then per destination a mailbox on its device
@@ -364,12 +365,12 @@ class ExpertParallel:
         with self._rank(d):
             self._after(sh, 0, d)
             if self.windows:
-                self._compute_windows(d, h, gate_up, down)
+                self._compute_windows(sh, d, h, gate_up, down)
             else:
                 self._compute_ops(sh, d, h, gate_up, down)
             self._mark(sh, 1, d)
 
-    def _compute_windows(self, d, h, gate_up, down):
+    def _compute_windows(self, sh, d, h, gate_up, down):
         from . import kernels
         chan, win = self._chan[d], self._win[d]
         inter = gate_up.shape[1] // 2
@@ -379,8 +380,13 @@ class ExpertParallel:
         mode = self.ops.mode
         if mode == "auto":  # from this rank's own batch: ranks may choose differently (no bit-identity promise)
             mode = kernels.auto_mode(h.shape[0] * self.R * self.k, self.E)
+        push = None
+        if not self.host_ordered:  # distinct GPUs: the dispatch rides in the expert launch's prologue
+            mine = sh["st"][d]
+            push = (mine["h"].data_ptr(), mine["token"].data_ptr(), mine["wsorted"].data_ptr(), mine["offsets"].data_ptr(),
+                    mine["h"].shape[0] * self.k)
         chan.experts(gate_up.data_ptr(), down.data_ptr(), 0 if mode == "gemv" else 1,
-                     torch.cuda.current_stream().cuda_stream)
+                     torch.cuda.current_stream().cuda_stream, push)
 
     def _compute_ops(self, sh, d, h, gate_up, down):
         ops, per, mine = self.ops, self.per, sh["st"][d]

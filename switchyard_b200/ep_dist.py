@@ -3,16 +3,14 @@ device-driven transport (csrc/ep.cu, host side in ep_window.py).
 
 `ep.ExpertParallel` keeps the reference's shape: one process drives all GPUs, a thread per rank.
 `DistributedExpertParallel` is the same transport for one process per GPU: every rank maps every
-other rank's window (CUDA IPC), a layer is four or five launches on the rank's stream (one for
-routing and sort up to 64 tokens, else router GEMM + route + sort), and the host never reads
-anything back:
+other rank's window (CUDA IPC), a layer is four launches on the rank's stream (five beyond 256
+tokens, where routing and sort are separate), and the host never reads anything back:
 
-    route_fused | router GEMM, route, sort        (local tokens, global expert ids)
-    ep_dispatch                                   rows -> owners' mailboxes; a receiver's arrival flag rises as
-                                                  soon as ITS rows are stored
-    ep_expert_ffn                                 waits for the arrival flags on the device, both projections;
-                                                  results stored straight into the senders' y; raises the
-                                                  senders' return flags when done
+    router GEMM, route + sort                     (local tokens, global expert ids)
+    ep_expert_ffn                                 prologue: this rank's rows -> owners' mailboxes, their arrival
+                                                  flags; waits for its own senders' flags on the device; both
+                                                  projections; results stored straight into the senders' y;
+                                                  raises the senders' return flags when done
     ep_combine                                    waits for all owners' return flags, sums in expert order
 
 The arithmetic per row and the order of the combine are those of the single-GPU layer with the
@@ -142,8 +140,9 @@ class DistributedExpertParallel:
         idx, _, _, offsets, token, wsorted, pos_of = self.backend.route_and_sort(h, self._placed(router), self.k, self.norm,
                                                                                  self.bias)
         with self.backend.stream() as stream:
-            self.chan.dispatch(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), N * self.k, stream)
-            self.chan.experts(gate_up.data_ptr(), down.data_ptr(), 1 if self.mode == "gemm" else 0, stream)
+            # the dispatch rides in the expert launch's prologue
+            self.chan.experts(gate_up.data_ptr(), down.data_ptr(), 1 if self.mode == "gemm" else 0, stream,
+                              push=(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), N * self.k))
             out = self.backend.empty((N, self.H), self.dtype)
             self.chan.combine(pos_of.data_ptr(), idx.data_ptr(), N, out.data_ptr(), stream)
         return out

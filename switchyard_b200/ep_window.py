@@ -75,12 +75,17 @@ class Channel:
                                            self.arrive_dst, self.p_counters, self.p_epoch, self.p_stats, stream),
                    "ep_dispatch", self.lib)
 
-    def experts(self, gate_up, down, compute_shape, stream):
-        """This rank's experts over everything in its mailbox; results go to the senders' y."""
+    def experts(self, gate_up, down, compute_shape, stream, push=None):
+        """This rank's experts over everything in its mailbox; results go to the senders' y.
+        push = (h, token, wsorted, offsets, rows): the layer's dispatch runs in this launch's
+        prologue instead of a launch of its own (do not call dispatch() then)."""
+        h, token, wsorted, offsets, rows = push if push is not None else (None, None, None, None, 0)
         _lib.check(self.lib.sy_ep_expert_ffn(self.p_x, self.p_w, self.p_meta, self.p_arrive, self.p_epoch, self.R,
                                              self.per, self.cap, gate_up, down, self.H, self.I, self.act, self.y_dst,
-                                             self.ret_dst, self.ffn_scratch, self.code, compute_shape, stream),
-                   "ep_expert_ffn", self.lib)
+                                             self.ret_dst, self.ffn_scratch, self.code, compute_shape, h, token, wsorted,
+                                             offsets, rows, self.rank, self.x_dst, self.w_dst, self.meta_dst,
+                                             self.arrive_dst, self.p_counters if push is not None else None,
+                                             self.p_stats, stream), "ep_expert_ffn", self.lib)
 
     def combine(self, pos_of, idx, n_tokens, out, stream):
         """Waits for every owner's results, then sums each token's rows into out [n_tokens, H]."""

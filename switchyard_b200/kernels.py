@@ -433,10 +433,12 @@ ROUTE_SORT_MAX_TOKENS = 256
 # route_fused (router GEMM inside the routing launch) is used up to this many tokens when asked for.
 ROUTE_FUSED_MAX_TOKENS = 64
 FUSED_ROUTER = os.environ.get("SWITCHYARD_FUSED_ROUTER") == "1"
-# From this many sorted rows the streaming mode folds the combine into the expert launch; below,
-# the separate combine kernel (overlapped by programmatic dependent launch) costs the same or less.
-# Measured on a B200 (OLMoE layer, graph replays): 64 tokens 129.9 against 131.4 us, 8 tokens equal.
-FUSED_COMBINE_MIN_ROWS = 256
+# The streaming mode can fold the combine into the expert launch (expert_ffn_combine: one launch
+# less). Measured on a B200 (OLMoE layer, graph replays) it does not pay: the expert launch gets
+# 4-6 us longer at 64 tokens (per tile a fence, an atomic per row and the re-read of finished
+# rows sit in the epilogue), while the separate combine kernel, overlapped by programmatic
+# dependent launch, adds 2.8 us. So it is off unless a caller lowers this row count.
+FUSED_COMBINE_MIN_ROWS = 1 << 30
 
 
 def fused_routing_applies(n_tokens, n_experts, hidden, top_k):
@@ -467,8 +469,7 @@ def route_and_sort(h, router, top_k, norm_topk_prob, bias=None, scratch=None, fu
 
 def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto", scratch=None):
     """route + experts (switchyard/kernels.py:91-93): router GEMM, routing + sort (one launch for
-    decode-sized batches), the expert FFN (one launch), combine (folded into the expert launch
-    for streaming-mode batches from 32 tokens)."""
+    decode-sized batches), the expert FFN (one launch), combine."""
     srt = route_and_sort(h, router, top_k, norm_topk_prob, scratch=scratch)
     return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
 
