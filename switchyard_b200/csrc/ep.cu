@@ -51,11 +51,11 @@ constexpr int EP_THREADS = 256;
 __global__ void __launch_bounds__(EP_THREADS)
 ep_dispatch_kernel(PushArgs p, int* epoch_counter, int* status) {
   __shared__ int s_seg[EP_MAX_RANKS + 1];
-  __shared__ int s_done;
+  __shared__ int s_done[2];
   pdl_launch_dependents();
   pdl_wait();  // offsets, token, wsorted come from the sort before this kernel
   const int epoch = *epoch_counter + 1;  // advanced below, once everything is stored
-  if (push_rows(p, epoch, status, s_seg, &s_done) && threadIdx.x == 0) {
+  if (push_rows(p, epoch, status, s_seg, s_done) && threadIdx.x == 0) {
     *epoch_counter = epoch;
     __threadfence();
   }
@@ -146,7 +146,9 @@ extern "C" int sy_ep_dispatch(const void* h, const int32_t* token, const void* w
   if (!status) return SY_ERR_CUDA;
   // rows_bound (the caller's sorted rows, known on the host) only sizes the grid; the kernel
   // takes the real row count from offsets
-  const int blocks = rows_bound < 1 ? 1 : (rows_bound < sms * 4 ? rows_bound : sms * 4);
+  const int per_block = EP_THREADS / 32;  // a warp per row
+  const int want = (rows_bound + per_block - 1) / per_block;
+  const int blocks = want < 1 ? 1 : (want < sms * 4 ? want : sms * 4);
   return launch_kernel(ep_dispatch_kernel, blocks, EP_THREADS, 0, static_cast<cudaStream_t>(stream), "ep_dispatch launch",
                        p, epoch_counter, status);
 }

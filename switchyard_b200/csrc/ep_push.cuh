@@ -28,13 +28,13 @@ struct PushArgs {
   long long* stats;                 // nullptr, or [0] += rows sent to other ranks, [1] += rows kept
 };
 
-// All threads of every block of the launch call this once. s_seg: R + 1 ints of shared memory.
-// Returns true in the block that completed the push (it has published the flags and reset the
-// counter).
+// All threads of every block of the launch call this once (the block size is a multiple of 32).
+// s_seg: R + 1 ints of shared memory; s_done: 2 ints. Returns true in the block that completed
+// the push (it has published the flags and reset the counter).
 __device__ __forceinline__ bool push_rows(const PushArgs& p, int epoch, int* status, int* s_seg, int* s_done) {
   const int R = p.R, per = p.per;
   if ((int)threadIdx.x <= R) s_seg[threadIdx.x] = p.offsets[threadIdx.x * per];
-  if (threadIdx.x == 0) *s_done = 0;
+  if (threadIdx.x == 0) s_done[0] = s_done[1] = 0;
   __syncthreads();
   const int rows = s_seg[R];
   int units = 0;
@@ -55,32 +55,46 @@ __device__ __forceinline__ bool push_rows(const PushArgs& p, int epoch, int* sta
       p.stats[1] += kept;
     }
   }
-  int d = 0;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    ++units;
+  // A warp per row, rows dealt to the warps of all blocks in turn: a row costs two dependent
+  // round trips (its token index, then its data), so what matters is how many rows are in
+  // flight, not how many threads copy one row.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  int mine = 0, d = 0;
+  for (int row = blockIdx.x * warps + warp; row < rows; row += gridDim.x * warps) {
+    ++mine;
     while (d + 1 < R && s_seg[d + 1] <= row) ++d;
     const int r = row - s_seg[d];
     if (r >= p.cap) {  // cannot happen when the caller respects its capacity; never write past a mailbox
-      if (threadIdx.x == 0) *status = DS_BAD_INDEX;
+      if (lane == 0) *status = DS_BAD_INDEX;
       continue;
     }
     const uint4* src = p.h + (size_t)p.token[row] * p.vec_per_row;
     uint4* dst = reinterpret_cast<uint4*>(p.x[d]) + (size_t)r * p.vec_per_row;
-    for (int i = threadIdx.x; i < p.vec_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
-    if (threadIdx.x == 0) reinterpret_cast<unsigned short*>(p.w[d])[r] = p.wsorted[row];
+    for (int i = lane; i < p.vec_per_row; i += 4 * 32) {  // four loads in flight per lane, then their stores
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (i + 32 * j < p.vec_per_row) v[j] = __ldg(src + i + 32 * j);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (i + 32 * j < p.vec_per_row) dst[i + 32 * j] = v[j];
+    }
+    if (lane == 0) reinterpret_cast<unsigned short*>(p.w[d])[r] = p.wsorted[row];
   }
+  if (lane == 0 && mine > 0) atomicAdd(s_done + 1, mine);
   __syncthreads();  // the block's stores have been issued
+  units += s_done[1];
   if (threadIdx.x == 0 && units > 0) {
     __threadfence_system();
     if (atomicAdd(p.counter, units) + units == rows + R) {
       __threadfence_system();
       for (int i = 0; i < R; ++i) st_release_sys(p.flag[i], epoch);
       *p.counter = 0;
-      *s_done = 1;
+      s_done[0] = 1;
     }
   }
   __syncthreads();
-  return *s_done != 0;
+  return s_done[0] != 0;
 }
 
 }  // namespace sy

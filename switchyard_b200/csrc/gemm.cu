@@ -531,7 +531,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
   __shared__ int s_flag_ok;
   __shared__ int s_epoch;
   __shared__ int s_push_seg[GM_MAX_RANKS + 1];
-  __shared__ int s_push_done;
+  __shared__ int s_push_done[2];
   __shared__ int s_final[GM_MAX_BN];       // fused combine: tokens this tile completes
   __shared__ int s_nfinal;
 
@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       s_flag_ok = 1;
       s_epoch = epoch;
     }
-    if (pushes) push_rows(args.ep.push, epoch, status, s_push_seg, &s_push_done);  // the layer's dispatch, in this launch
+    if (pushes) push_rows(args.ep.push, epoch, status, s_push_seg, s_push_done);  // the layer's dispatch, in this launch
     __syncthreads();
     if ((int)threadIdx.x < R && !wait_flag(args.ep.arrive + threadIdx.x, epoch, GM_WAIT_NS)) {
       *status = DS_TIMEOUT_FLAG;
