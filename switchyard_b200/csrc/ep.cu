@@ -36,6 +36,7 @@
 //
 // Replaces the per-pair gather + three copies + event of switchyard/ep.py:193-223, the
 // per-segment ffn + copy back + event of l.239-262, and the event waits of l.264-272.
+#include <stdlib.h>
 #include <string.h>
 
 #include "combine.cuh"
@@ -120,6 +121,14 @@ int make_push_args(PushArgs* out, const char* name, const void* h, const int32_t
                name, d);
   }
   p.counter = counter;
+  // SY_PUSH_FENCE=sys in the environment (read once): every block fences at system scope before it
+  // counts its rows, instead of at GPU scope with one system-scope fence by the completing block
+  // (3 us slower per layer on a B200; kept as a conservative switch)
+  static const int fence_sys = [] {
+    const char* v = getenv("SY_PUSH_FENCE");
+    return v && v[0] == 's' ? 1 : 0;
+  }();
+  p.block_fence_sys = fence_sys;
   p.stats = reinterpret_cast<long long*>(stats);
   *out = p;
   return SY_OK;

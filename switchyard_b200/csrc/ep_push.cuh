@@ -24,6 +24,7 @@ struct PushArgs {
   unsigned char* w[EP_MAX_RANKS];   // ... router weights
   int* meta[EP_MAX_RANKS];          // ... [per+1 rebased offsets | first row | row count]
   int* flag[EP_MAX_RANKS];          // ... arrival flag of this sender
+  int block_fence_sys;              // 1: every block fences at system scope before it counts; 0: at GPU scope
   int* counter;                     // [1] units stored so far (rows + one per destination); zero between launches
   long long* stats;                 // nullptr, or [0] += rows sent to other ranks, [1] += rows kept
 };
@@ -85,7 +86,13 @@ __device__ __forceinline__ bool push_rows(const PushArgs& p, int epoch, int* sta
   __syncthreads();  // the block's stores have been issued
   units += s_done[1];
   if (threadIdx.x == 0 && units > 0) {
-    __threadfence_system();
+    // Release: this block's stores (ordered before this thread by the barrier) before its count.
+    // The count is an atomic in this GPU's memory read by blocks of this GPU only, so GPU scope
+    // orders it; the block that completes the total then fences at system scope before it raises
+    // the flags in the receivers' memory, which carries every block's stores along (the chain of
+    // release/acquire pairs is transitive whatever the scope of each link).
+    if (p.block_fence_sys) __threadfence_system();
+    else __threadfence();
     if (atomicAdd(p.counter, units) + units == rows + R) {
       __threadfence_system();
       for (int i = 0; i < R; ++i) st_release_sys(p.flag[i], epoch);
