@@ -177,7 +177,7 @@ sort_single_kernel(const int* __restrict__ idx, const T* __restrict__ w, int m, 
 // Replaces switchyard/kernels.py:30-32 (cuBLAS GEMM, then route) and moe_kernels.cu:142-157.
 constexpr int RF_TOKENS = 16;
 
-template <typename T>
+template <typename T, bool GEMM>
 __global__ void __launch_bounds__(SORT_THREADS)
 route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const T* __restrict__ bias,
                    const T* __restrict__ logits_in, int n_tokens, int E,
@@ -194,7 +194,7 @@ route_fused_kernel(const T* __restrict__ h, const T* __restrict__ router, const 
   pdl_launch_dependents();
   pdl_wait();  // the hidden states (or the logits) come from the caller's previous kernel
 
-  if (logits_in) {
+  if constexpr (!GEMM) {
     // the logits are given (sy_route_sort): a warp per token straight from global memory
     if (t0 + warp < n_tokens)
       route_token_any<T>(logits_in + (size_t)(t0 + warp) * E, E, k, norm, lane, idx + (size_t)(t0 + warp) * k,
@@ -428,31 +428,28 @@ static int launch_route_fused(const void* h, const void* router, const void* bia
   const size_t smem = sort_smem > gemm_smem ? sort_smem : gemm_smem;
   const int blocks = (n_tokens + RF_TOKENS - 1) / RF_TOKENS;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // only the form with the GEMM inside needs more than the default 48 KB of dynamic shared memory
   static std::atomic<int> configured[MAX_DEVICES][2];
   int dev = 0;
   SY_CUDA(cudaGetDevice(&dev));
   const int which = dtype == SY_DTYPE_F16 ? 0 : 1;
-  if (!configured[dev][which].load(std::memory_order_acquire)) {
+  if (!logits_in && !configured[dev][which].load(std::memory_order_acquire)) {
     const size_t most = (size_t)SORT_WARPS * RF_TOKENS * ROUTE_MAX_E * sizeof(float);
     if (which == 0)
-      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
     else
-      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+      SY_CUDA(cudaFuncSetAttribute(route_fused_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
     configured[dev][which].store(1, std::memory_order_release);
   }
-  if (dtype == SY_DTYPE_F16)
-    return launch_kernel(route_fused_kernel<__half>, blocks, SORT_THREADS, smem, s, "route_fused launch",
-                         static_cast<const __half*>(h), static_cast<const __half*>(router),
-                         static_cast<const __half*>(bias), static_cast<const __half*>(logits_in), n_tokens, n_experts,
-                         hidden, top_k, norm, sh.per_block, static_cast<__half*>(logits_out), idx,
-                         static_cast<__half*>(w), counts, offsets, token, static_cast<__half*>(wsorted), pos_of, ticket,
-                         status);
-  return launch_kernel(route_fused_kernel<__nv_bfloat16>, blocks, SORT_THREADS, smem, s, "route_fused launch",
-                       static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(router),
-                       static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(logits_in), n_tokens,
-                       n_experts, hidden, top_k, norm, sh.per_block, static_cast<__nv_bfloat16*>(logits_out), idx,
-                       static_cast<__nv_bfloat16*>(w), counts, offsets, token, static_cast<__nv_bfloat16*>(wsorted),
-                       pos_of, ticket, status);
+#define SY_RF_LAUNCH(TYPE, GEMM)                                                                                         \
+  launch_kernel(route_fused_kernel<TYPE, GEMM>, blocks, SORT_THREADS, smem, s, "route_fused launch",                      \
+                static_cast<const TYPE*>(h), static_cast<const TYPE*>(router), static_cast<const TYPE*>(bias),            \
+                static_cast<const TYPE*>(logits_in), n_tokens, n_experts, hidden, top_k, norm, sh.per_block,              \
+                static_cast<TYPE*>(logits_out), idx, static_cast<TYPE*>(w), counts, offsets, token,                       \
+                static_cast<TYPE*>(wsorted), pos_of, ticket, status)
+  if (dtype == SY_DTYPE_F16) return logits_in ? SY_RF_LAUNCH(__half, false) : SY_RF_LAUNCH(__half, true);
+  return logits_in ? SY_RF_LAUNCH(__nv_bfloat16, false) : SY_RF_LAUNCH(__nv_bfloat16, true);
+#undef SY_RF_LAUNCH
 }
 }  // namespace sy
 
