@@ -508,6 +508,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] (MODE gemv | gemm | ep) - run one small layer shape (for profiling)")
+    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
+                    help="expert placement for --config ep256 / prefill on several GPUs: contiguous blocks, or dealt out "
+                         "by the measured per-expert load (switchyard_b200.placement.balanced)")
     ap.add_argument("--config", default="decode", choices=["decode", "ep256", "prefill", "model"],
                     help="decode = the bench line (configs[1]); ep256 / prefill / model = configs[2] / configs[3] / configs[4]")
     args = ap.parse_args()

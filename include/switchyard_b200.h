@@ -285,7 +285,13 @@ int sy_ep_dispatch(const void* h, const int32_t* token, const void* wsorted, con
  * x_dst .. flag_dst, counters and stats; the layer's epoch is then *epoch_counter + 1 and the
  * launch advances *epoch_counter when it ends. With push_counter == NULL a sy_ep_dispatch before
  * it has done both (the form for ranks that share one GPU and order their steps by events).
- * act: 16-bit [n_ranks*capacity, inter] scratch. scratch: as sy_expert_ffn. */
+ * compute_shape: 0 = streaming shape; 1 / 2 = compute shape with the single-CTA / CTA-pair tile,
+ * an expert's ranges sharing its tiles (rows gathered with 16-byte copies); 3 / 4 = the same
+ * tiles with every sender's rows of an expert tiled on their own: a range is contiguous in the
+ * mailbox, so its rows arrive as TMA boxes (about 30 % faster when a sender brings hundreds of
+ * rows per expert; more padding when it brings few). The results are the same bits in all forms.
+ * act: 16-bit [n_ranks*capacity, inter] scratch. scratch: sy_expert_ffn_scratch_bytes(n_ranks *
+ * experts_per_rank) bytes, zero before the first call, left zero. */
 int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const int32_t* meta, const int32_t* arrive_flags,
                      int32_t* epoch_counter, int n_ranks, int experts_per_rank, int capacity, const void* gate_up,
                      const void* down, int hidden, int inter, void* act, void* const* y_dst,

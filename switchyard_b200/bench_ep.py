@@ -25,29 +25,36 @@ LAYERS = 8
 METRIC, UNIT = "moe_layer_decode_expert_weight_GBps", "GB/s"
 
 
-def rank_weights(device, dtype, seed, lo, hi):
-    """Experts [lo, hi) of the weight set `seed` (same values as synthetic.layer_weights gives
-    for the whole set: the generator is advanced past the experts this rank does not hold)."""
+def rank_weights(device, dtype, seed, lo, hi, experts=None):
+    """Experts [lo, hi) of the weight set `seed`, or the listed `experts` in that order (same
+    values as synthetic.layer_weights gives for the whole set: the generator is advanced past the
+    experts this rank does not hold)."""
+    mine = list(range(lo, hi)) if experts is None else [int(e) for e in experts]
+    slot = {e: i for i, e in enumerate(mine)}
     g = torch.Generator(device=device).manual_seed(seed)
     router = (torch.randn(E, H, device=device, generator=g) * 0.02).to(dtype)
-    gate_up = torch.empty(hi - lo, 2 * I, H, device=device, dtype=dtype)
-    down = torch.empty(hi - lo, H, I, device=device, dtype=dtype)
-    for e in range(hi):
+    gate_up = torch.empty(len(mine), 2 * I, H, device=device, dtype=dtype)
+    down = torch.empty(len(mine), H, I, device=device, dtype=dtype)
+    for e in range(max(mine) + 1):
         a = torch.randn(2 * I, H, device=device, generator=g)
         b = torch.randn(H, I, device=device, generator=g)
-        if e >= lo:
-            gate_up[e - lo] = (a * 0.02).to(dtype)
-            down[e - lo] = (b * 0.02).to(dtype)
+        if e in slot:
+            gate_up[slot[e]] = (a * 0.02).to(dtype)
+            down[slot[e]] = (b * 0.02).to(dtype)
     return router, gate_up, down
 
 
-def check_bit_identity(ep, kernels, layer, full, hs, rank, world):
+def check_bit_identity(ep, kernels, layer, full, hs, rank, world, order=None):
     """Every rank's expert-parallel output against the single-GPU layer on the same tokens with
-    the whole expert set (same mode): must be the same bits. Collective; returns (ok on every
-    rank, rows each rank sent / kept during the check)."""
+    the whole expert set (same mode): must be the same bits. With a placement the single-GPU
+    layer gets its experts (and router rows) in placement order, so that a token's expert
+    outputs are added in the same order on both sides. Collective; returns (ok on every rank,
+    rows each rank sent / kept during the check)."""
     ok = True
+    if order is not None:
+        full = (full[0][order].contiguous(), full[1][order].contiguous(), full[2][order].contiguous())
     for h in hs:
-        got = ep.layer(h, *layer)
+        got = ep.layer(h, layer[0], layer[1], layer[2])
         want = kernels.moe_layer_with_bias(h, full[0], full[1], full[2], TOPK, False, ep.mode, ep.bias)
         torch.cuda.synchronize()
         ok = ok and bool(torch.equal(got, want))
@@ -244,8 +251,27 @@ def run_config(args):
         dtype, sizes, mode = torch.bfloat16, (1024, 4096, 8192), "gemm"
     per = E // world
     n_sets = 3
-    layers = [rank_weights(dev, dtype, 100 + l, rank * per, (rank + 1) * per) for l in range(n_sets)]
     bias = synthetic.zipf_bias()
+    # --placement balanced: measure the per-expert load of this configuration's routing on every
+    # rank (largest batch, routing only), add it up over the ranks, and deal the experts out so
+    # that every rank computes about the same number of rows (switchyard_b200.placement)
+    place, balance = None, None
+    if world > 1 and getattr(args, "placement", "contiguous") == "balanced":
+        from . import placement as pl
+        router0 = rank_weights(dev, dtype, 100, 0, 1)[0]
+        hb = synthetic.hidden_states(sizes[-1], dev, dtype, seed=1000 * rank + sizes[-1])
+        meter = pl.LoadMeter(E, dev)
+        meter.add(kernels.route_and_sort(hb, router0, TOPK, False, bias.to(dev).to(dtype))[2])
+        dist.all_reduce(meter.total)
+        load = meter.read()
+        place = pl.balanced(load, world)
+        balance = {"rows_per_rank_contiguous": pl.rank_rows(load, pl.contiguous(E), world).tolist(),
+                   "rows_per_rank_balanced": pl.rank_rows(load, place, world).tolist(),
+                   "imbalance_contiguous": pl.imbalance(pl.rank_rows(load, pl.contiguous(E), world)),
+                   "imbalance_balanced": pl.imbalance(pl.rank_rows(load, place, world))}
+        del hb, meter
+    mine = None if place is None else place[rank * per:(rank + 1) * per]
+    layers = [rank_weights(dev, dtype, 100 + l, rank * per, (rank + 1) * per, mine) for l in range(n_sets)]
     out = []
     for T in sizes:
         h = synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T)
@@ -253,9 +279,9 @@ def run_config(args):
             from .ep_dist import DistributedExpertParallel
             m = kernels.auto_mode(T * world * TOPK, E)
             ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode=m, device=dev,
-                                           logit_bias=bias)
+                                           logit_bias=bias, placement=place)
             full = synthetic.layer_weights(dev, dtype, seed=100)
-            identical, rows_rank = check_bit_identity(ep, kernels, layers[0], full, [h], rank, world)
+            identical, rows_rank = check_bit_identity(ep, kernels, layers[0], full, [h], rank, world, place)
             del full
             torch.cuda.empty_cache()
             if not identical:
@@ -311,6 +337,7 @@ def run_config(args):
                     "rows_sent_kept_per_rank": rows_rank})
     if rank == 0:
         print(json.dumps({"config": args.config, "n_gpus": world, "dtype": str(dtype).replace("torch.", ""),
+                          "placement": getattr(args, "placement", "contiguous"), "balance": balance,
                           "steps": args.steps, "timing": "CUDA events around CUDA-graph replays of the whole layer, max over ranks",
                           "results": out, "device_status": kernels.ext().device_status(dev)}), flush=True)
     if world > 1:

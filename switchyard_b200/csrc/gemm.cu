@@ -156,6 +156,8 @@ struct KernelArgs {
   const int* ends;
   const unsigned long long* c_table;     // [ranges] optional per-range output row pointers
   int ranges, group_div;                 // expert e owns ranges [e*group_div, (e+1)*group_div)
+  int weight_div;                        // the weights of "expert" e (a group of ranges) are those of expert
+                                         // e / weight_div: > 1 when an expert's ranges are tiled separately
   int n_problems;                        // 1, or 2 = fused FFN: p[1] reads what p[0] wrote
   int* ready;                            // fused: [experts] finished p[0] tiles, then [1] blocks that have left
   int* status;
@@ -674,7 +676,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       const Tile tile = locate_tile<BN>(t, tiles0, seen, cursor, s_tile_start, s_rows);
       const Problem& P = args.p[tile.phase];
       const int Nfull = P.swiglu ? 2 * P.Nout : P.Nout;
-      const int y0 = tile.e * Nfull + wbase_of(tile);
+      const int y0 = (tile.e / args.weight_div) * Nfull + wbase_of(tile);
       const int y1 = P.swiglu ? y0 + P.Nout : y0 + S::BOX_ROWS;
       const int k_blocks = k_blocks_of(tile.phase);
       // contiguous token rows: the tile's first row in A (rows past the tile's end belong to the
@@ -1083,6 +1085,8 @@ struct GroupedArgs {
   const unsigned long long* c_table;
   int ranges;              // number of row ranges (experts x ranges per expert)
   int group_div;           // ranges per expert: ranges [e*group_div, (e+1)*group_div) are expert e's rows
+  int weight_div;          // 0 / 1: a group of ranges is an expert; n: n consecutive groups share an expert's weights
+  int forced_shape;        // -1: chosen here; else SH_PAIR / SH_DUO as the caller asked
   int32_t* ready;          // fused FFN scratch: experts + 1 ints, zero before the first launch
   int rows;                // upper bound of the row indices in begins / ends
   int dtype;
@@ -1141,7 +1145,9 @@ static int launch_gemm(const GroupedArgs& a) {
   memset(&k, 0, sizeof(k));
   k.status = device_status_word();
   if (!k.status) return SY_ERR_CUDA;
-  const int experts = a.ranges / a.group_div;
+  const int weight_div = a.weight_div > 1 ? a.weight_div : 1;
+  const int experts = a.ranges / a.group_div / weight_div;
+  k.weight_div = weight_div;
   for (int i = 0; i < a.n_problems; ++i) {
     const ProblemDesc& d = a.p[i];
     rc = weight_map(&k.p[i].map, d.B, (uint64_t)experts * (d.swiglu ? 2 : 1) * d.n_out, (uint64_t)d.k_dim, a.dtype,
@@ -1199,6 +1205,7 @@ static int forced_tile() {
   return f;
 }
 static int compute_shape_for(const GroupedArgs& a, int rows) {
+  if (a.forced_shape == SH_PAIR || a.forced_shape == SH_DUO) return a.forced_shape;
   bool plain = a.group_div == 1 && !a.ep.arrive;
   for (int i = 0; i < a.n_problems; ++i) plain = plain && !a.p[i].a_rows && !a.p[i].use_table;
   if (plain && forced_tile() >= 0) return forced_tile();
@@ -1248,6 +1255,7 @@ static GroupedArgs single(const void* A, const int32_t* a_rows, const void* B, c
   memset(&a, 0, sizeof(a));
   a.p[0] = ProblemDesc{A, a_rows, B, n_out, k_dim, swiglu, scale, C, c_table != nullptr};
   a.n_problems = 1;
+  a.forced_shape = -1;
   a.begins = begins;
   a.ends = ends;
   a.c_table = c_table;
@@ -1267,6 +1275,7 @@ static GroupedArgs ffn_pair(const void* x, const int32_t* a_rows, const void* ga
   a.p[0] = ProblemDesc{x, a_rows, gate_up, inter, hidden, 1, nullptr, act, 0};
   a.p[1] = ProblemDesc{act, nullptr, down, hidden, inter, 0, wsorted, y, y_through_table};
   a.n_problems = 2;
+  a.forced_shape = -1;
   a.ready = scratch;
   a.dtype = dtype;
   a.stream = static_cast<cudaStream_t>(stream);
@@ -1373,11 +1382,22 @@ extern "C" int sy_ep_expert_ffn(const void* x_mail, const void* w_mail, const in
   using namespace sy;
   SY_REQUIRE(n_ranks >= 1 && n_ranks <= GM_MAX_RANKS && experts_per_rank >= 1 && capacity >= 1,
              "ep_expert_ffn: 1..%d ranks (got %d)", GM_MAX_RANKS, n_ranks);
+  SY_REQUIRE(compute_shape >= 0 && compute_shape <= 4, "ep_expert_ffn: compute_shape 0..4 (got %d)", compute_shape);
   SY_REQUIRE(x_mail && w_mail && meta && arrive_flags && epoch_counter && y_dst && ret_flag_dst,
              "ep_expert_ffn: null pointer");
   GroupedArgs a = ffn_pair(x_mail, nullptr, gate_up, down, hidden, inter, w_mail, act, nullptr, 1, scratch, dtype, stream);
   a.ranges = n_ranks * experts_per_rank;
   a.group_div = n_ranks;
+  if (compute_shape >= 3) {
+    // every sender's rows of an expert are tiled on their own: a range is then contiguous in the
+    // mailbox, its token rows come as TMA boxes, and its tiles follow the expert's other ranges
+    // (the weights are re-read from L2)
+    a.group_div = 1;
+    a.weight_div = n_ranks;
+    a.forced_shape = compute_shape == 3 ? SH_PAIR : SH_DUO;
+  } else if (compute_shape == 2) {
+    a.forced_shape = SH_DUO;
+  }
   a.ep.arrive = arrive_flags;
   a.ep.meta = meta;
   a.ep.epoch_counter = epoch_counter;

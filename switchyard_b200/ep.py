@@ -256,7 +256,7 @@ class ExpertParallel:
             wins = []
             for r, dev in enumerate(self.devices):
                 t = torch.zeros(lay["total"], dtype=torch.uint8, device=dev)
-                wins.append({"mem": t, "ffn": torch.zeros(self.per + 1, dtype=torch.int32, device=dev), "act": None,
+                wins.append({"mem": t, "ffn": torch.zeros(self.E + 1, dtype=torch.int32, device=dev), "act": None,
                              "stats": t[lay["stats"]:lay["stats"] + 16].view(torch.int64),
                              "y": t[lay["y"]:lay["y"] + cap * H * elem].view(dtype).view(cap, H)})
             for dev in set(self.devices):
@@ -385,7 +385,7 @@ class ExpertParallel:
             mine = sh["st"][d]
             push = (mine["h"].data_ptr(), mine["token"].data_ptr(), mine["wsorted"].data_ptr(), mine["offsets"].data_ptr(),
                     mine["h"].shape[0] * self.k)
-        chan.experts(gate_up.data_ptr(), down.data_ptr(), 0 if mode == "gemv" else 1,
+        chan.experts(gate_up.data_ptr(), down.data_ptr(), chan.shape_code(mode, h.shape[0]),
                      torch.cuda.current_stream().cuda_stream, push)
 
     def _compute_ops(self, sh, d, h, gate_up, down):

@@ -113,7 +113,7 @@ class DistributedExpertParallel:
             self._opened.append((p.value, off))
         # local scratch of the compute phase
         self.act = self.backend.empty((self.R * self.cap, inter), dtype)
-        self.ffn_scratch = self.backend.zeros(self.per + 1, torch.int32)
+        self.ffn_scratch = self.backend.zeros(self.E + 1, torch.int32)
         code = _lib.SY_DTYPE_F16 if dtype == torch.float16 else _lib.SY_DTYPE_BF16
         self.chan = Channel(self.lib, self.rank, self.R, self.per, top_k, hidden, inter, self.cap, self.cap, self.elem,
                             code, bases, act=self.act.data_ptr(), ffn_scratch=self.ffn_scratch.data_ptr())
@@ -141,7 +141,7 @@ class DistributedExpertParallel:
                                                                                  self.bias)
         with self.backend.stream() as stream:
             # the dispatch rides in the expert launch's prologue
-            self.chan.experts(gate_up.data_ptr(), down.data_ptr(), 1 if self.mode == "gemm" else 0, stream,
+            self.chan.experts(gate_up.data_ptr(), down.data_ptr(), self.chan.shape_code(self.mode, N), stream,
                               push=(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), N * self.k))
             out = self.backend.empty((N, self.H), self.dtype)
             self.chan.combine(pos_of.data_ptr(), idx.data_ptr(), N, out.data_ptr(), stream)

@@ -68,6 +68,19 @@ class Channel:
         self.p_meta, self.p_w, self.p_x, self.p_y = base + lay["meta"], base + lay["w"], base + lay["x"], base + lay["y"]
         self.act, self.ffn_scratch = act, ffn_scratch
 
+    # From this many rows per expert and sender the compute shape tiles every sender's rows of an
+    # expert on their own (contiguous in the mailbox: TMA boxes) instead of gathering an expert's
+    # rows from all senders into shared tiles; from PAIR_ROWS with CTA pairs.
+    SPLIT_ROWS, PAIR_ROWS = 192, 768
+
+    def shape_code(self, mode, n_tokens):
+        """compute_shape of sy_ep_expert_ffn for a layer in which the ranks bring about n_tokens
+        tokens each."""
+        if mode == "gemv":
+            return 0
+        per_range = n_tokens * self.k / (self.per * self.R)
+        return 4 if per_range >= self.PAIR_ROWS else 3 if per_range >= self.SPLIT_ROWS else 1
+
     def dispatch(self, h, token, wsorted, offsets, rows, stream):
         """Rows of h (picked through token[], sorted by global expert) into the owners' mailboxes."""
         _lib.check(self.lib.sy_ep_dispatch(h, token, wsorted, offsets, rows, self.per, self.R, self.rank,

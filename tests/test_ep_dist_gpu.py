@@ -118,7 +118,9 @@ def test_one_rank_equals_the_single_gpu_layer(mode, dtype_name):
 
 def test_one_rank_at_the_benchmark_shape():
     run(1, [(64,), (256,), (8,)], "gemv", shape=OLMOE, zipf=True)
-    run(1, [(300,)], "gemm", shape=OLMOE, zipf=True)
+    # compute shape: 300 tokens share tiles across senders; from 192 rows per expert and sender the
+    # senders' rows are tiled on their own (TMA rows), from 768 with CTA pairs
+    run(1, [(300,), (2048,), (6200,)], "gemm", shape=OLMOE, zipf=True)
 
 
 def test_one_rank_with_a_placement():

@@ -519,6 +519,15 @@ def test_graphed_layer_replays_the_same_bits(K):
             torch.cuda.synchronize()
             assert torch.equal(out, want.cpu())
     assert len(layer.graphs) == 3
+    # the same pair of pinned buffers again: the copies are inside the replayed graph
+    hin = torch.empty(40, rd.shape[1], dtype=torch.float16).pin_memory()
+    hout = torch.empty(40, rd.shape[1], dtype=torch.float16).pin_memory()
+    for seed in (5, 6, 7):
+        hin.copy_(torch.randn(40, rd.shape[1], generator=cases.gen(seed)).half())
+        assert layer(hin, out=hout) is hout
+        torch.cuda.synchronize()
+        assert torch.equal(hout, K.moe_layer(hin.to(DEV), rd, gud, dnd, 8, False, "auto").cpu())
+    assert len(layer.staged) == 1
     layer.check()  # no replayed kernel gave up on a wait
 
 
