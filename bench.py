@@ -235,23 +235,18 @@ def run_single_gpu(args):
             used[(T, l)] = int(torch.unique(idx).numel())
     torch.cuda.synchronize()
 
-    # one CUDA graph per (T, layer): the whole layer, router GEMM to combine
+    # warm-up of every (T, weight set) combination: library load, cuBLAS kernel choice, scratch
     stream = torch.cuda.Stream(dev)
-    graphs, outs = {}, {}
+    outs = {}
     with torch.cuda.stream(stream):
         for T in SWEEP:
-            for l, (router, gu, dn) in enumerate(layers):
+            for router, gu, dn in layers:
                 for _ in range(2):
                     kernels.moe_layer(hs[T], router, gu, dn, TOPK, False, mode)
-                stream.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    outs[(T, l)] = kernels.moe_layer(hs[T], router, gu, dn, TOPK, False, mode)
-                graphs[(T, l)] = g
-    torch.cuda.synchronize()
+        stream.synchronize()
     assert kernels.ext().device_status(dev) == 0
 
-    # one CUDA graph per STEP as well: the four passes of a step back to back, as the layers of a
+    # one CUDA graph per STEP: the four passes of a step back to back, as the layers of a
     # decode loop run (a pass starts while its predecessor drains); a step starting at weight set
     # 0 and one starting at set 4, replayed alternately, so that no pass finds its weights in L2
     step_graphs, step_bytes = [], []
@@ -285,30 +280,30 @@ def run_single_gpu(args):
     total_bytes = sum(step_bytes[i % len(step_graphs)] for i in range(args.steps))
     value = total_bytes / (total_ms / 1e3) / 1e9
 
-    # ---- per batch size: the same layer passes replayed one graph at a time, an event pair around
-    # each (includes the replay's own launch latency, which the step graphs above do not pay)
-    per_T_ms = {T: 0.0 for T in SWEEP}
-    per_T_bytes = {T: 0 for T in SWEEP}
-    pass_no = [0]
-    all_evs = []
+    # ---- per batch size: one graph per T holding that T's pass over each of the eight weight sets
+    # back to back (what a decode loop's consecutive layers look like); K replays per T
+    sweep = []
     with torch.cuda.stream(stream):
-        for rep in range(args.warmup + args.steps):
-            for T in SWEEP:
-                l = pass_no[0] % LAYERS
-                pass_no[0] += 1
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                graphs[(T, l)].replay()
-                b.record(stream)
-                if rep >= args.warmup:
-                    all_evs.append((T, l, a, b))
-        stream.synchronize()
-    for T, l, a, b in all_evs:
-        per_T_ms[T] += a.elapsed_time(b)
-        per_T_bytes[T] += used[(T, l)] * EXPERT_BYTES
-    sweep = [{"tokens": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
-              "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
-              "experts_used_mean": per_T_bytes[T] / EXPERT_BYTES / args.steps} for T in SWEEP]
+        for T in SWEEP:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for l, (router, gu, dn) in enumerate(layers):
+                    outs[("sweep", T, l)] = kernels.moe_layer(hs[T], router, gu, dn, TOPK, False, mode)
+            for _ in range(max(args.warmup // 2, 2)):
+                g.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(args.steps):
+                g.replay()
+            b.record(stream)
+            stream.synchronize()
+            ms = a.elapsed_time(b)
+            nbytes = sum(used[(T, l)] for l in range(LAYERS)) * EXPERT_BYTES * args.steps
+            sweep.append({"tokens": T, "us_per_layer": ms / (args.steps * LAYERS) * 1e3,
+                          "expert_weight_GBps": nbytes / (ms / 1e3) / 1e9,
+                          "of_nominal_8TBps": nbytes / (ms / 1e3) / 1e9 / 8000.0,
+                          "experts_used_mean": sum(used[(T, l)] for l in range(LAYERS)) / LAYERS})
+            del g
 
     # ---- end to end through the public API with host buffers: kernels.GraphedLayer, the layer as
     # a decode loop holds it (launches captured once per batch size); every step copies its
@@ -317,6 +312,8 @@ def run_single_gpu(args):
     host_out = {T: torch.empty(T, H, dtype=dtype).pin_memory() for T in SWEEP}
     with torch.cuda.stream(stream):
         graphed = [kernels.GraphedLayer(router, gu, dn, TOPK, False, mode) for router, gu, dn in layers]
+
+    pass_no = [0]
 
     def e2e_step():
         nbytes = 0
@@ -368,7 +365,7 @@ def run_single_gpu(args):
     assert ext.device_status(dev) == 0
 
     # ---- prefill: the same layer, compute-bound (bf16, Zipf-skewed routing), graph replays
-    del graphs, step_graphs, graphed, outs, layers
+    del step_graphs, graphed, outs, layers
     torch.cuda.empty_cache()
     prefill = prefill_leg(dev, stream, steps=max(args.steps // 2, 6))
 
@@ -385,7 +382,8 @@ def run_single_gpu(args):
         "arm": {"mode": mode, "path": "router GEMM (library) -> route + sort (one launch) -> expert FFN (tcgen05 weight "
                                       "stream, both projections in one launch) -> combine",
                 "timing": "CUDA events on the launch stream around K replays of CUDA graphs holding one step "
-                          "(the four layer passes back to back); `sweep` times each pass's own graph separately"},
+                          "(the four layer passes back to back); `sweep`: per T, replays of one graph holding "
+                          "that T's pass over each of the eight weight sets"},
         "sweep": sweep,
         "vs_nominal_8TBps": value / 8000.0,
         "clocks": clocks,

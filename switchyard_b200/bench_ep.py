@@ -105,60 +105,71 @@ def run(args):
     stream = torch.cuda.Stream(dev)
     pass_no = [0]
 
-    # one CUDA graph per (T, weight set) holding the whole expert-parallel layer; every rank
-    # builds and replays them in the same order
-    graphs, outs = {}, {}
+    # warm-up, then one CUDA graph per STEP (the four passes of a step back to back, a step starting
+    # at weight set 0 and one at set 4) and, for the per-T breakdown, one graph per T holding that
+    # T's pass over each of the eight weight sets; every rank builds and replays them in the same order
+    keep = []
     with torch.cuda.stream(stream):
         for T in SWEEP:
-            for l, (router, gu, dn) in enumerate(layers):
+            for router, gu, dn in layers:
                 ep.layer(hs[T], router, gu, dn)
         stream.synchronize()
         dist.barrier()
+        step_graphs, step_bytes = [], []
+        for first in range(0, LAYERS, len(SWEEP)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i, T in enumerate(SWEEP):
+                    keep.append(ep.layer(hs[T], *layers[(first + i) % LAYERS]))
+            step_graphs.append(g)
+            step_bytes.append(sum(used[(T, (first + i) % LAYERS)] for i, T in enumerate(SWEEP)) * EXPERT_BYTES)
+        t_graphs = {}
         for T in SWEEP:
-            for l, (router, gu, dn) in enumerate(layers):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    outs[(T, l)] = ep.layer(hs[T], router, gu, dn)
-                graphs[(T, l)] = g
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for l in range(LAYERS):
+                    keep.append(ep.layer(hs[T], *layers[l]))
+            t_graphs[T] = g
     torch.cuda.synchronize()
     dist.barrier()
 
-    def step(timed, evs):
-        for T in SWEEP:
-            l = pass_no[0] % LAYERS
-            pass_no[0] += 1
-            if timed:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-            graphs[(T, l)].replay()
-            if timed:
-                b.record(stream)
-                evs.append((T, l, a, b))
-
     with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            step(False, None)
+        for i in range(args.warmup):
+            step_graphs[i % len(step_graphs)].replay()
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
         sampler = bench.ClockSampler(dev.index).__enter__() if rank == 0 else None
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        evs = []
         t0.record(stream)
-        for _ in range(args.steps):
-            step(True, evs)
+        for i in range(args.steps):
+            step_graphs[i % len(step_graphs)].replay()
         t1.record(stream)
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler else None
-    times = torch.tensor([t0.elapsed_time(t1)] + [sum(a.elapsed_time(b) for (T2, _, a, b) in evs if T2 == T) for T in SWEEP],
-                         dtype=torch.float64, device=dev)
+        clocks = sampler.stop() if sampler else None
+        per_T = []
+        for T in SWEEP:
+            for _ in range(2):
+                t_graphs[T].replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(args.steps):
+                t_graphs[T].replay()
+            b.record(stream)
+            torch.cuda.synchronize()
+            per_T.append(a.elapsed_time(b))
+            dist.barrier()
+    times = torch.tensor([t0.elapsed_time(t1)] + per_T, dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms = float(times[0])
     per_T_ms = {T: float(times[1 + i]) for i, T in enumerate(SWEEP)}
-    per_T_bytes = {T: sum(used[(T2, l)] for (T2, l, _, _) in evs if T2 == T) * EXPERT_BYTES for T in SWEEP}
-    total_bytes = sum(per_T_bytes.values())
+    per_T_bytes = {T: sum(used[(T, l)] for l in range(LAYERS)) * EXPERT_BYTES * args.steps for T in SWEEP}
+    total_bytes = sum(step_bytes[i % len(step_graphs)] for i in range(args.steps))
+    del step_graphs, t_graphs, keep
 
     # end to end with host buffers
     host_in = {T: hs[T].cpu().pin_memory() for T in SWEEP}
@@ -209,14 +220,16 @@ def run(args):
             "arm": {"mode": mode, "parallelism": f"ep{world}: {per} experts per GPU, T tokens PER GPU (weak scaling in "
                                                  "tokens), attention data-parallel; dispatch and return by kernels "
                                                  "writing into peer memory, no collective on the data path",
-                    "timing": "CUDA events on each rank's stream around CUDA-graph replays of the whole layer, max over ranks"},
+                    "timing": "CUDA events on each rank's stream around K replays of CUDA graphs holding one step (the four "
+                              "layer passes back to back), max over ranks; `sweep`: per T, replays of one graph holding "
+                              "that T's pass over each of the eight weight sets"},
             "ep_bit_identical": identical,
             "ep_check": {"what": "every rank's layer output == kernels.moe_layer on its own tokens with all 64 experts, "
                                  "T=1,8,32,64, torch.equal, before timing",
                          "rows_sent_kept_per_rank": check_rows},
-            "sweep": [{"tokens_per_gpu": T, "us_per_layer": per_T_ms[T] / args.steps * 1e3,
+            "sweep": [{"tokens_per_gpu": T, "us_per_layer": per_T_ms[T] / (args.steps * LAYERS) * 1e3,
                        "expert_weight_GBps": per_T_bytes[T] / (per_T_ms[T] / 1e3) / 1e9,
-                       "tokens_per_s": T * world * args.steps / (per_T_ms[T] / 1e3)} for T in SWEEP],
+                       "tokens_per_s": T * world * args.steps * LAYERS / (per_T_ms[T] / 1e3)} for T in SWEEP],
             "clocks": clocks,
             "e2e": {"value": e2e_bytes / (float(e2e_t) / 1e3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": io_bytes,
                     "d2h_bytes_per_step": io_bytes, "ms_per_step": float(e2e_t) / args.steps,

@@ -527,7 +527,7 @@ def test_graphed_layer_replays_the_same_bits(K):
         assert layer(hin, out=hout) is hout
         torch.cuda.synchronize()
         assert torch.equal(hout, K.moe_layer(hin.to(DEV), rd, gud, dnd, 8, False, "auto").cpu())
-    assert len(layer.staged) == 1
+    assert (40, hin.data_ptr(), hout.data_ptr()) in layer.staged
     layer.check()  # no replayed kernel gave up on a wait
 
 
