@@ -506,6 +506,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] (MODE gemv | gemm | ep) - run one small layer shape (for profiling)")
+    ap.add_argument("--mode", default="auto", choices=["auto", "gemv", "gemm"],
+                    help="kernel mode for --config ep256 / prefill (auto: by rows per expert)")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
                     help="expert placement for --config ep256 / prefill on several GPUs: contiguous blocks, or dealt out "
                          "by the measured per-expert load (switchyard_b200.placement.balanced)")

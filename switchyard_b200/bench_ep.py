@@ -290,7 +290,7 @@ def run_config(args):
         h = synthetic.hidden_states(T, dev, dtype, seed=1000 * rank + T)
         if world > 1:
             from .ep_dist import DistributedExpertParallel
-            m = kernels.auto_mode(T * world * TOPK, E)
+            m = kernels.auto_mode(T * world * TOPK, E) if getattr(args, "mode", "auto") == "auto" else args.mode
             ep = DistributedExpertParallel(E, TOPK, False, H, I, max_tokens=T, dtype=dtype, mode=m, device=dev,
                                            logit_bias=bias, placement=place)
             full = synthetic.layer_weights(dev, dtype, seed=100)
