@@ -508,6 +508,9 @@ def main():
     ap.add_argument("--case", default=None, help="MODE:T[:bf16][:zipf] (MODE gemv | gemm | ep) - run one small layer shape (for profiling)")
     ap.add_argument("--mode", default="auto", choices=["auto", "gemv", "gemm"],
                     help="kernel mode for --config ep256 / prefill (auto: by rows per expert)")
+    ap.add_argument("--host", default="processes", choices=["processes", "threads"],
+                    help="--config ep256 only: one process per GPU under torchrun (ep_dist, graph replays), or ONE process "
+                         "driving --gpus N GPUs with a thread each (ep.ExpertParallel, the reference's shape; run without torchrun)")
     ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
                     help="expert placement for --config ep256 / prefill on several GPUs: contiguous blocks, or dealt out "
                          "by the measured per-expert load (switchyard_b200.placement.balanced)")
@@ -523,6 +526,8 @@ def main():
         sys.exit("bench.py needs a CUDA GPU (there is no CPU path); use --impl reference for the CPU baseline")
     if args.config != "decode":
         from switchyard_b200 import bench_ep
+        if args.config == "ep256" and args.host == "threads":
+            return bench_ep.run_threads(args)
         return bench_ep.run_model(args) if args.config == "model" else bench_ep.run_config(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single_gpu(args)

@@ -358,6 +358,59 @@ def run_config(args):
 
 
 # ------------------------------------------------------------------------------------------
+# configs[2] through the reference-shaped host: ONE process, a thread and a stream per GPU
+# (`ep.ExpertParallel.layer_threaded`), 256 tokens per GPU, fp16, Zipf routing. Launches are eager
+# (a layer driven by several host threads is not captured in one graph), so the figure includes
+# the host's launch cost; `bench.py --config ep256` under torchrun is the one-process-per-GPU
+# form of the same layer, replayed from graphs.
+def run_threads(args):
+    import time
+    from . import kernels, synthetic
+    from .ep import CudaOps, ExpertParallel
+
+    n = args.gpus
+    if torch.cuda.device_count() < n:
+        raise SystemExit(f"--host threads needs {n} visible GPUs in this process")
+    devices = [torch.device("cuda", i) for i in range(n)]
+    dtype, T = torch.float16, 256
+    per = E // n
+    mode = kernels.auto_mode(T * n * TOPK, E) if args.mode == "auto" else args.mode
+    bias = synthetic.zipf_bias()
+    sets = 3
+    weights = [[rank_weights(d, dtype, 100 + l, r * per, (r + 1) * per) for r, d in enumerate(devices)] for l in range(sets)]
+    hs = [synthetic.hidden_states(T, d, dtype, seed=1000 * r + T) for r, d in enumerate(devices)]
+    ep = ExpertParallel(devices, E, TOPK, False, ops=CudaOps(mode, logit_bias=bias))
+    ep.reserve(T)
+
+    def layer(l):
+        w = weights[l % sets]
+        return ep.layer_threaded(hs, [x[0] for x in w], [x[1] for x in w], [x[2] for x in w])
+
+    # bit-identity against the single-GPU layer on rank 0's tokens
+    full = synthetic.layer_weights(devices[0], dtype, seed=100)
+    want = kernels.moe_layer_with_bias(hs[0], full[0], full[1], full[2], TOPK, False, mode, bias.to(devices[0]).to(dtype))
+    identical = bool(torch.equal(layer(0)[0], want))
+    del full
+    for i in range(max(args.warmup, 3)):
+        layer(i)
+    for d in devices:
+        torch.cuda.synchronize(d)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        layer(i)
+    for d in devices:
+        torch.cuda.synchronize(d)
+    ms = (time.perf_counter() - t0) / args.steps * 1e3
+    ep.check()
+    rows = T * n * TOPK
+    print(json.dumps({"config": "ep256", "host": "one process, a thread per GPU (ep.ExpertParallel.layer_threaded), eager launches",
+                      "n_gpus": n, "dtype": "float16", "mode": mode, "steps": args.steps, "tokens_per_gpu": T,
+                      "ms_per_layer": ms, "tokens_per_s": T * n / (ms / 1e3), "tflops_per_gpu": rows * 12582912 / (ms / 1e3) / 1e12 / n,
+                      "timing": "host wall clock around K layers, all GPUs synchronised before and after",
+                      "ep_bit_identical_rank0": identical, "stats": ep.stats}), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
 # config 5: the full random-init OLMoE-1B-7B architecture, fp16: 128-token prompts of uniform
 # random ids, 32 greedy decode tokens, `batch` requests dealt round-robin to the ranks
 # (attention data-parallel, experts expert-parallel). tok/s = batch * new / wall(generate),
