@@ -1,5 +1,5 @@
-"""The one-process-per-rank expert-parallel protocol (switchyard_b200.ep_dist) in two and four
-real processes over gloo, without a GPU: the device side is replaced by the host-memory mock of
+"""The one-process-per-rank expert-parallel protocol (switchyard_b200.ep_dist) in two, four
+and eight real processes over gloo, without a GPU: the device side is replaced by the host-memory mock of
 oracle/ep_dist_mock.py (windows in /dev/shm mapped by the peers, polling flag waits), so what
 runs is the product's own host logic: window layout, pointer tables, argument order, device-side
 epochs, mailbox reuse over several layers, a rank with zero tokens, a permuted expert placement.
@@ -64,7 +64,8 @@ PLACEMENT = [5, 12, 0, 9, 3, 14, 7, 1, 10, 2, 15, 6, 11, 4, 13, 8]
 
 @pytest.mark.parametrize("world,sizes,placement", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], None),
                                                    (2, [(5, 9), (0, 3), (1, 0)], PLACEMENT),
-                                                   (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None)])
+                                                   (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None),
+                                                   (8, [(2, 0, 5, 1, 3, 4, 0, 6), (4,) * 8], None)])
 def test_protocol_over_gloo_processes(world, sizes, placement):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
