@@ -148,7 +148,6 @@ def run(args):
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
-        clocks = sampler.stop() if sampler else None
         per_T = []
         for T in SWEEP:
             for _ in range(2):
@@ -163,6 +162,7 @@ def run(args):
             torch.cuda.synchronize()
             per_T.append(a.elapsed_time(b))
             dist.barrier()
+        clocks = sampler.stop() if sampler else None
     times = torch.tensor([t0.elapsed_time(t1)] + per_T, dtype=torch.float64, device=dev)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms = float(times[0])
