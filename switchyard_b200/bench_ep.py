@@ -58,13 +58,13 @@ def check_bit_identity(ep, kernels, layer, full, hs, rank, world, order=None):
         want = kernels.moe_layer_with_bias(h, full[0], full[1], full[2], TOPK, False, ep.mode, ep.bias)
         torch.cuda.synchronize()
         ok = ok and bool(torch.equal(got, want))
-    verdict = torch.tensor([1 if ok else 0], device=hs[0].device)
-    dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    agreed = torch.tensor([1 if ok else 0], device=hs[0].device)
+    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
     sent, kept = ep.row_counts()
     rows = torch.zeros(world, 2, dtype=torch.int64, device=hs[0].device)
     rows[rank, 0], rows[rank, 1] = sent, kept
     dist.all_reduce(rows)
-    return bool(int(verdict)), rows.tolist()
+    return bool(int(agreed)), rows.tolist()
 
 
 def run(args):

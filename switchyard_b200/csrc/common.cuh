@@ -194,10 +194,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
 }
 
 // ---- flags between GPUs ---------------------------------------------------------------------
-// A flag is an int in one GPU's memory that another GPU's kernel release-stores an ever-growing
-// epoch into; the owner's kernels wait until it has reached the epoch they expect.
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// A flag is an int in one GPU's memory that another GPU's kernel stores an ever-growing epoch
+// into (after a system-scope fence); the owner's kernels wait until it has reached the epoch they expect.
+// The writer fences at system scope once and then stores every peer's flag relaxed: fence +
+// relaxed store is a release, and the stores leave back to back, where a st.release per flag
+// would first wait until the store before it has been acknowledged by its GPU (a round trip
+// over NVLink per flag).
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;

@@ -3,7 +3,7 @@
 // rows too, locally) together with the router weight; block 0 adds, per destination, the
 // rebased per-expert offsets, the segment's first row and its row count. Every block counts what
 // it has stored (one system-scope fence and one atomic per block); the block that completes the
-// total release-stores the layer's epoch into every receiver's arrival flag.
+// total fences at system scope and stores the layer's epoch into every receiver's arrival flag.
 // Used by the stand-alone dispatch kernel (ep.cu) and by the expert kernel's prologue (gemm.cu),
 // which saves a launch on the layer's critical path.
 #pragma once
@@ -95,7 +95,7 @@ __device__ __forceinline__ bool push_rows(const PushArgs& p, int epoch, int* sta
     else __threadfence();
     if (atomicAdd(p.counter, units) + units == rows + R) {
       __threadfence_system();
-      for (int i = 0; i < R; ++i) st_release_sys(p.flag[i], epoch);
+      for (int i = 0; i < R; ++i) st_relaxed_sys(p.flag[i], epoch);  // released by the fence above
       *p.counter = 0;
       s_done[0] = 1;
     }

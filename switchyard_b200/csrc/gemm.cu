@@ -1002,7 +1002,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_umma_kernel(const __grid_c
       if (args.ep.arrive) {
         __threadfence_system();
         const int epoch = s_epoch;
-        for (int r = 0; r < args.ep.R; ++r) st_release_sys(args.ep.ret_flag[r], epoch);
+        for (int r = 0; r < args.ep.R; ++r) st_relaxed_sys(args.ep.ret_flag[r], epoch);  // released by the fence above
         if (args.ep.push.counter) *args.ep.epoch_counter = epoch;  // the combine that follows reads it
         __threadfence();
       } else {
