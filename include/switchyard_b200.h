@@ -213,6 +213,13 @@ int sy_expert_ffn_combine(const void* x, const int32_t* token, const void* gate_
 int sy_combine(const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
                void* out, int dtype, void* stream);
 
+/* combine_add — sy_combine followed by the caller's residual add (switchyard/model.py:135,
+ * `x = x + self.moe(i, h)`) in the same launch: out[t, :] = round16( float(residual[t, :]) +
+ * float(round16(sum)) ), the bits of the 16-bit addition done separately. residual 16-bit
+ * [n_tokens, hidden], 16-byte aligned; out may be residual itself. */
+int sy_combine_add(const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
+                   const void* residual, void* out, int dtype, void* stream);
+
 /* gather_rows — replaces `gather_rows` (moe_kernels.cu:459-467, kernel l.450-457).
  * dst[row, :] = src[index[row], :] for row < n; row_bytes % 16 == 0. dst may be memory of a
  * peer GPU (peer access enabled, or an IPC mapping): the dispatch store. */
@@ -314,6 +321,11 @@ int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_counter, int ep
 int sy_ep_combine(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
                   const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out, int dtype,
                   void* stream);
+
+/* ep_combine_add — sy_ep_combine with the residual add of sy_combine_add in the same launch. */
+int sy_ep_combine_add(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
+                      const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
+                      const void* residual, void* out, int dtype, void* stream);
 
 /* ipc_export / ipc_open / ipc_close — map one rank's window into another process (CUDA IPC).
  * export: 64-byte handle of the allocation containing ptr and ptr's offset in it.

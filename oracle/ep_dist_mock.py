@@ -167,6 +167,15 @@ class _Lib:
             _view(ret_flag_dst[s], 1, np.int32)[0] = epoch
         return 0
 
+    def sy_ep_combine_add(self, ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, residual, out,
+                          dtype, stream):
+        rc = self.sy_ep_combine(ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, out, dtype, stream)
+        if rc == 0 and n_tokens:
+            dt = torch.float16 if dtype == 0 else torch.bfloat16
+            o = _torch16(_addr(out), n_tokens, hidden, dt)
+            o.copy_(_torch16(_addr(residual), n_tokens, hidden, dt) + o)  # the 16-bit addition done separately
+        return rc
+
     def sy_ep_combine(self, ret_flags, R, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden, out, dtype, stream):
         if not self._wait(ret_flags, R, int(_view(epoch_counter, 1, np.int32)[0])):
             return -3

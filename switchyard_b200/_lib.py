@@ -48,6 +48,7 @@ SYMBOLS = {
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                                       c_void_p]),
     "sy_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "sy_combine_add": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "sy_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "sy_copy_async": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "sy_enable_peer_access": (c_int, [c_int, c_int, ctypes.POINTER(c_int)]),
@@ -63,6 +64,8 @@ SYMBOLS = {
     "sy_ep_wait": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "sy_ep_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                               c_int, c_void_p]),
+    "sy_ep_combine_add": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                  c_void_p, c_int, c_void_p]),
     "sy_ipc_export": (c_int, [c_void_p, c_void_p, ctypes.POINTER(ctypes.c_uint64)]),
     "sy_ipc_open": (c_int, [c_void_p, ctypes.c_uint64, ctypes.POINTER(c_void_p)]),
     "sy_ipc_close": (c_int, [c_void_p, ctypes.c_uint64]),

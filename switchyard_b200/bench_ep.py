@@ -440,11 +440,12 @@ def run_model(args):
             from .ep_dist import DistributedExpertParallel
             ep = DistributedExpertParallel(c.experts, c.top_k, c.norm_topk_prob, c.hidden, c.intermediate,
                                            max_tokens=mine * plen, dtype=dtype, mode="auto", device=dev)
-            moe = lambda i, h: ep.layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"], w["layers"][i]["down"])
+            moe = lambda i, h, x: ep.layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
+                                           w["layers"][i]["down"], residual=x)
         else:
-            moe = lambda i, h: kernels.moe_layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
-                                                 w["layers"][i]["down"], c.top_k, c.norm_topk_prob)
-        dec = olmoe.Decoder(c, w, moe)
+            moe = lambda i, h, x: kernels.moe_layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
+                                                    w["layers"][i]["down"], c.top_k, c.norm_topk_prob, residual=x)
+        dec = olmoe.Decoder(c, w, moe, moe_adds_residual=True)  # the residual add rides in the combine launch
         session = olmoe.Session(dec, mine, plen + new)
         dec.generate(prompts, 4, graph=True, session=session)  # warm-up: libraries, allocator, graph capture
         torch.cuda.synchronize()

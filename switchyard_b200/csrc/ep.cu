@@ -77,14 +77,14 @@ template <typename T>
 __global__ void __launch_bounds__(COMBINE_THREADS)
 ep_combine_kernel(const int* ret_flags, int R, const int* epoch_counter, const T* __restrict__ y,
                   const int* __restrict__ pos_of, const int* __restrict__ idx, int n_tokens, int k, int H,
-                  T* __restrict__ out, int* status, unsigned long long wait_ns) {
+                  T* __restrict__ out, const T* __restrict__ residual, int* status, unsigned long long wait_ns) {
   __shared__ int s_row[COMBINE_MAX_K];
   pdl_launch_dependents();
   pdl_wait();
   const int epoch = *epoch_counter;
   if ((int)threadIdx.x < R && !wait_flag(ret_flags + threadIdx.x, epoch, wait_ns)) *status = DS_TIMEOUT_FLAG;
   __syncthreads();
-  if ((int)blockIdx.x < n_tokens) combine_token<T, true>(y, pos_of, idx, k, H, out, blockIdx.x, s_row, n_tokens * k);
+  if ((int)blockIdx.x < n_tokens) combine_token<T, true>(y, pos_of, idx, k, H, out, blockIdx.x, s_row, n_tokens * k, residual);
 }
 
 }  // namespace sy
@@ -171,16 +171,17 @@ extern "C" int sy_ep_wait(const int32_t* flags, int n, const int32_t* epoch_coun
                        epoch_counter, epoch_offset, status, (unsigned long long)wait_limit_ns());
 }
 
-extern "C" int sy_ep_combine(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
-                             const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out,
-                             int dtype, void* stream) {
-  using namespace sy;
-  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && ret_flags && epoch_counter, "ep_combine: bad arguments");
-  SY_REQUIRE(n_tokens >= 0 && top_k >= 1 && top_k <= COMBINE_MAX_K, "ep_combine: top_k must be 1..8 (got %d)", top_k);
-  SY_REQUIRE(hidden > 0 && hidden % 8 == 0, "ep_combine: hidden must be a multiple of 8 (got %d)", hidden);
-  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "ep_combine: dtype must be f16 or bf16");
-  SY_REQUIRE(n_tokens == 0 || (y && pos_of && idx && out), "ep_combine: null pointer");
-  SY_REQUIRE(((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0), "ep_combine: y and out must be 16-byte aligned");
+namespace sy {
+static int ep_combine_launch(const char* name, const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter,
+                             const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k,
+                             int hidden, const void* residual, bool wants_residual, void* out, int dtype, void* stream) {
+  SY_REQUIRE(n_ranks >= 1 && n_ranks <= EP_MAX_RANKS && ret_flags && epoch_counter, "%s: bad arguments", name);
+  SY_REQUIRE(n_tokens >= 0 && top_k >= 1 && top_k <= COMBINE_MAX_K, "%s: top_k must be 1..8 (got %d)", name, top_k);
+  SY_REQUIRE(hidden > 0 && hidden % 8 == 0, "%s: hidden must be a multiple of 8 (got %d)", name, hidden);
+  SY_REQUIRE(dtype == SY_DTYPE_F16 || dtype == SY_DTYPE_BF16, "%s: dtype must be f16 or bf16", name);
+  SY_REQUIRE(n_tokens == 0 || (y && pos_of && idx && out && (residual || !wants_residual)), "%s: null pointer", name);
+  SY_REQUIRE(((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual % 16 == 0),
+             "%s: y, residual and out must be 16-byte aligned", name);
   int* status = device_status_word();
   if (!status) return SY_ERR_CUDA;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -189,10 +190,25 @@ extern "C" int sy_ep_combine(const int32_t* ret_flags, int n_ranks, const int32_
   if (dtype == SY_DTYPE_F16)
     return launch_kernel(ep_combine_kernel<__half>, blocks, COMBINE_THREADS, 0, s, "ep_combine launch", ret_flags, n_ranks,
                          epoch_counter, static_cast<const __half*>(y), pos_of, idx, n_tokens, top_k, hidden,
-                         static_cast<__half*>(out), status, wait_ns);
+                         static_cast<__half*>(out), static_cast<const __half*>(residual), status, wait_ns);
   return launch_kernel(ep_combine_kernel<__nv_bfloat16>, blocks, COMBINE_THREADS, 0, s, "ep_combine launch", ret_flags,
                        n_ranks, epoch_counter, static_cast<const __nv_bfloat16*>(y), pos_of, idx, n_tokens, top_k, hidden,
-                       static_cast<__nv_bfloat16*>(out), status, wait_ns);
+                       static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(residual), status, wait_ns);
+}
+}  // namespace sy
+
+extern "C" int sy_ep_combine(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
+                             const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden, void* out,
+                             int dtype, void* stream) {
+  return sy::ep_combine_launch("ep_combine", ret_flags, n_ranks, epoch_counter, y, pos_of, idx, n_tokens, top_k, hidden,
+                               nullptr, false, out, dtype, stream);
+}
+
+extern "C" int sy_ep_combine_add(const int32_t* ret_flags, int n_ranks, const int32_t* epoch_counter, const void* y,
+                                 const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
+                                 const void* residual, void* out, int dtype, void* stream) {
+  return sy::ep_combine_launch("ep_combine_add", ret_flags, n_ranks, epoch_counter, y, pos_of, idx, n_tokens, top_k,
+                               hidden, residual, true, out, dtype, stream);
 }
 
 // ---- CUDA IPC helpers: how the ranks' windows are mapped into one another (set-up time) ----

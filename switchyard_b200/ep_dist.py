@@ -129,11 +129,16 @@ class DistributedExpertParallel:
             hit = self._routers[id(router)] = (router, router[self.perm].contiguous())
         return hit[1]
 
-    def layer(self, h, router, gate_up, down):
+    def layer(self, h, router, gate_up, down, residual=None):
         """h [N,H] this rank's tokens (N <= max_tokens, may be 0); router [E,H] (replicated, rows
         in the model's expert order); gate_up [E/R,2I,H], down [E/R,H,I]: this rank's experts.
-        Returns [N,H]. Collective: every rank must call it once per layer, in the same order."""
+        Returns [N,H]; with residual [N,H] (contiguous, h's dtype) residual + layer(h), added in the
+        combine launch with the bits of the separate 16-bit addition. Collective: every rank must
+        call it once per layer, in the same order."""
         N = h.shape[0]
+        if residual is not None and (residual.shape != h.shape or residual.dtype != h.dtype
+                                     or not residual.is_contiguous()):
+            raise RuntimeError("layer: residual must be contiguous, of h's shape and dtype")
         if N > self.max_tokens:
             raise RuntimeError(f"layer: {N} tokens exceed max_tokens={self.max_tokens}")
         h = h.contiguous()
@@ -144,7 +149,8 @@ class DistributedExpertParallel:
             self.chan.experts(gate_up.data_ptr(), down.data_ptr(), self.chan.shape_code(self.mode, N), stream,
                               push=(h.data_ptr(), token.data_ptr(), wsorted.data_ptr(), offsets.data_ptr(), N * self.k))
             out = self.backend.empty((N, self.H), self.dtype)
-            self.chan.combine(pos_of.data_ptr(), idx.data_ptr(), N, out.data_ptr(), stream)
+            self.chan.combine(pos_of.data_ptr(), idx.data_ptr(), N, out.data_ptr(), stream,
+                              residual.data_ptr() if residual is not None else None)
         return out
 
     def row_counts(self):

@@ -100,7 +100,13 @@ class Channel:
                                              self.arrive_dst, self.p_counters if push is not None else None,
                                              self.p_stats, stream), "ep_expert_ffn", self.lib)
 
-    def combine(self, pos_of, idx, n_tokens, out, stream):
-        """Waits for every owner's results, then sums each token's rows into out [n_tokens, H]."""
-        _lib.check(self.lib.sy_ep_combine(self.p_ret, self.R, self.p_epoch, self.p_y, pos_of, idx, n_tokens, self.k,
-                                          self.H, out, self.code, stream), "ep_combine", self.lib)
+    def combine(self, pos_of, idx, n_tokens, out, stream, residual=None):
+        """Waits for every owner's results, then sums each token's rows into out [n_tokens, H];
+        residual (an address, optional): [n_tokens, H] added to the rounded sums in the same launch."""
+        if residual is None:
+            rc = self.lib.sy_ep_combine(self.p_ret, self.R, self.p_epoch, self.p_y, pos_of, idx, n_tokens, self.k,
+                                        self.H, out, self.code, stream)
+        else:
+            rc = self.lib.sy_ep_combine_add(self.p_ret, self.R, self.p_epoch, self.p_y, pos_of, idx, n_tokens, self.k,
+                                            self.H, residual, out, self.code, stream)
+        _lib.check(rc, "ep_combine", self.lib)

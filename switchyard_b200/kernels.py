@@ -273,16 +273,26 @@ class Ext:
     def grouped_gemv(self, A, a_rows, B, offsets, rows, swiglu, scale):
         return self._grouped(self.lib.sy_grouped_gemv, "grouped_gemv", A, a_rows, B, offsets, rows, swiglu, scale)
 
-    def combine(self, y, pos_of, idx, n_tokens):
+    def combine(self, y, pos_of, idx, n_tokens, residual=None):
+        """residual [n_tokens, H] (optional, y's dtype): returns residual + combine(...) from the same
+        launch, with the bits of the separate 16-bit addition."""
         _check(y, "y"), _check(pos_of, "pos_of"), _check(idx, "idx")
         code = _dtype_code(y, "combine")
         H, k = y.shape[1], idx.shape[1]
         out = torch.empty(n_tokens, H, dtype=y.dtype, device=y.device)
+        if residual is not None:
+            _check(residual, "residual")
+            if residual.shape != out.shape or residual.dtype != y.dtype:
+                raise RuntimeError("combine: residual must be [n_tokens, hidden] in y's dtype")
         if n_tokens == 0:
             return out
         with _Device(y.device) as stream:
-            _lib.check(self.lib.sy_combine(_ptr(y), _ptr(pos_of), _ptr(idx), int(n_tokens), k, H, _ptr(out), code, stream),
-                       "combine")
+            if residual is None:
+                rc = self.lib.sy_combine(_ptr(y), _ptr(pos_of), _ptr(idx), int(n_tokens), k, H, _ptr(out), code, stream)
+            else:
+                rc = self.lib.sy_combine_add(_ptr(y), _ptr(pos_of), _ptr(idx), int(n_tokens), k, H, _ptr(residual),
+                                             _ptr(out), code, stream)
+            _lib.check(rc, "combine")
         return out
 
     def gather_rows(self, src, index, dst):
@@ -404,16 +414,18 @@ def ffn(x, a_rows, offsets, counts, wsorted, gate_up, down, rows, mode, host_cou
     raise RuntimeError(f"ffn: unknown mode {mode!r}")
 
 
-def _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch=None):
-    """From sorted choices (idx, w, counts, offsets, token, wsorted, pos_of) to the layer's output."""
+def _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch=None, residual=None):
+    """From sorted choices (idx, w, counts, offsets, token, wsorted, pos_of) to the layer's output
+    (plus the residual, when given)."""
     idx, _, counts, offsets, token, wsorted, pos_of = srt
     if mode == "auto":
         mode = auto_mode(idx.numel(), gate_up.shape[0])  # no device-to-host read
     if mode == "gemv" and 0 < top_k <= 8 and idx.numel() >= FUSED_COMBINE_MIN_ROWS:
         # streaming shape: the combine rides in the down projection's epilogue (one launch)
-        return ext().expert_ffn_combine(h.contiguous(), token, gate_up, down, offsets, wsorted, pos_of, top_k, scratch)
+        out = ext().expert_ffn_combine(h.contiguous(), token, gate_up, down, offsets, wsorted, pos_of, top_k, scratch)
+        return out if residual is None else residual + out
     y = ffn(h, token, offsets, counts, wsorted, gate_up, down, idx.numel(), mode, scratch=scratch)
-    return ext().combine(y, pos_of, idx, h.shape[0])
+    return ext().combine(y, pos_of, idx, h.shape[0], residual)
 
 
 def experts(h, idx, w, gate_up, down, mode="auto"):
@@ -467,18 +479,20 @@ def route_and_sort(h, router, top_k, norm_topk_prob, bias=None, scratch=None, fu
     return [idx, w] + X.sort_by_expert(idx, w, E)
 
 
-def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto", scratch=None):
+def moe_layer(h, router, gate_up, down, top_k, norm_topk_prob, mode="auto", scratch=None, residual=None):
     """route + experts (switchyard/kernels.py:91-93): router GEMM, routing + sort (one launch for
-    decode-sized batches), the expert FFN (one launch), combine."""
+    decode-sized batches), the expert FFN (one launch), combine. residual [N,H] (optional, beyond
+    the reference's signature): returns residual + layer(h), the caller's `x + self.moe(i, h)`
+    (switchyard/model.py:135) from the combine launch, same bits as the separate addition."""
     srt = route_and_sort(h, router, top_k, norm_topk_prob, scratch=scratch)
-    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
+    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch, residual)
 
 
-def moe_layer_with_bias(h, router, gate_up, down, top_k, norm_topk_prob, mode, bias, scratch=None):
+def moe_layer_with_bias(h, router, gate_up, down, top_k, norm_topk_prob, mode, bias, scratch=None, residual=None):
     """moe_layer with a per-expert bias [E] (h's dtype) added to the router logits before routing:
     how the benchmarks apply their synthetic routing skew."""
     srt = route_and_sort(h, router, top_k, norm_topk_prob, bias, scratch)
-    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch)
+    return _sorted_experts(h, srt, gate_up, down, top_k, mode, scratch, residual)
 
 
 class GraphedLayer:

@@ -149,10 +149,12 @@ class Cache:
 
 
 class Decoder:
-    """OLMoE decoder with an MoE hook. moe(i, h): h [B*T, H] -> [B*T, H]."""
+    """OLMoE decoder with an MoE hook. moe(i, h): h [B*T, H] -> [B*T, H]. With
+    moe_adds_residual=True the hook is moe(i, h, x) and returns x + layer(h) itself (x [B*T, H]
+    contiguous: `kernels.moe_layer(..., residual=x)` does the addition in its combine launch)."""
 
-    def __init__(self, config, weights, moe):
-        self.c, self.w, self.moe = config, weights, moe
+    def __init__(self, config, weights, moe, moe_adds_residual=False):
+        self.c, self.w, self.moe, self.moe_adds_residual = config, weights, moe, moe_adds_residual
         c = config
         embed = weights["embed"]
         self.rope = RotaryTable(c.head_dim, c.rope_theta, c.max_positions, embed.dtype, embed.device)
@@ -171,6 +173,12 @@ class Decoder:
             q, k, v = (t.clamp(-c.clip_qkv, c.clip_qkv) for t in (q, k, v))
         heads = lambda t, n: t.reshape(B, T, n, c.head_dim).transpose(1, 2)
         return rotate(heads(q, c.heads), cos, sin), rotate(heads(k, c.kv_heads), cos, sin), heads(v, c.kv_heads)
+
+    def _after_moe(self, i, h, x):
+        """x + moe layer i of h, for x [B, T, H] and h [B*T, H]."""
+        if self.moe_adds_residual:
+            return self.moe(i, h, x.reshape(h.shape).contiguous()).view(x.shape)
+        return x + self.moe(i, h).view(x.shape)
 
     def _attend(self, L, q, k, v, mask):
         c = self.c
@@ -211,7 +219,7 @@ class Decoder:
                 k, v = cache.k[i][:, :, :start + T], cache.v[i][:, :, :start + T]
             x = x + self._attend(L, q, k, v, mask)
             h = scaled_norm(x, L["mlp_norm"], c.rms_eps).reshape(B * T, -1)
-            x = x + self.moe(i, h).view(B, T, -1)
+            x = self._after_moe(i, h, x)
         if cache is not None:
             cache.length += T
             cache.next_pos += valid.long().sum(1)
@@ -237,7 +245,7 @@ class Decoder:
             cache.v[i].index_copy_(2, at, v)
             x = x + self._attend(L, q, cache.k[i], cache.v[i], mask)
             h = scaled_norm(x, L["mlp_norm"], c.rms_eps).reshape(B, -1)
-            x = x + self.moe(i, h).view(B, 1, -1)
+            x = self._after_moe(i, h, x)
         cache.length += 1
         cache.next_pos += 1
         return F.linear(scaled_norm(x, W["final_norm"], c.rms_eps), W["lm_head"])[:, 0]

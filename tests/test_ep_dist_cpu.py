@@ -2,7 +2,7 @@
 and eight real processes over gloo, without a GPU: the device side is replaced by the host-memory mock of
 oracle/ep_dist_mock.py (windows in /dev/shm mapped by the peers, polling flag waits), so what
 runs is the product's own host logic: window layout, pointer tables, argument order, device-side
-epochs, mailbox reuse over several layers, a rank with zero tokens, a permuted expert placement.
+epochs, mailbox reuse over several layers, a rank with zero tokens, a permuted expert placement, the residual handed to the combine.
 Every rank's output must equal the one-process layer computed with the same row-at-a-time
 arithmetic."""
 
@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, sizes_per_layer, placement, out):
+def _rank_main(rank, world, port, sizes_per_layer, placement, residual, out):
     import torch.distributed as dist
     from oracle import ep_dist_mock as mock
     from switchyard_b200.ep_dist import DistributedExpertParallel
@@ -45,8 +45,10 @@ def _rank_main(rank, world, port, sizes_per_layer, placement, out):
         ok, sent = True, 0
         for layer_no, sizes in enumerate(sizes_per_layer):
             h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).half()
-            got = ep.layer(h, router, my_gu, my_dn)
-            ok = ok and torch.equal(got, mock.single_layer(h, router[order], gu[order], dn[order], k, False))
+            x = torch.randn(h.shape, generator=cases.gen(7 + layer_no)).half() if residual else None
+            got = ep.layer(h, router, my_gu, my_dn, residual=x)
+            want = mock.single_layer(h, router[order], gu[order], dn[order], k, False)
+            ok = ok and torch.equal(got, want if x is None else x + want)
         sent, kept = ep.row_counts()
         ok = ok and sent + kept == sum(s[rank] for s in sizes_per_layer) * k
         ep.close()
@@ -62,16 +64,16 @@ def _rank_main(rank, world, port, sizes_per_layer, placement, out):
 PLACEMENT = [5, 12, 0, 9, 3, 14, 7, 1, 10, 2, 15, 6, 11, 4, 13, 8]
 
 
-@pytest.mark.parametrize("world,sizes,placement", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], None),
-                                                   (2, [(5, 9), (0, 3), (1, 0)], PLACEMENT),
-                                                   (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None),
-                                                   (8, [(2, 0, 5, 1, 3, 4, 0, 6), (4,) * 8], None)])
-def test_protocol_over_gloo_processes(world, sizes, placement):
+@pytest.mark.parametrize("world,sizes,placement,residual", [(2, [(5, 9), (0, 3), (12, 12), (1, 0)], None, False),
+                                                            (2, [(5, 9), (0, 3), (1, 0)], PLACEMENT, True),
+                                                            (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None, False),
+                                                            (8, [(2, 0, 5, 1, 3, 4, 0, 6), (4,) * 8], None, False)])
+def test_protocol_over_gloo_processes(world, sizes, placement, residual):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, placement, out)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, placement, residual, out)) for r in range(world)]
     for p in procs:
         p.start()
     results = [out.get(timeout=180) for _ in procs]

@@ -75,9 +75,12 @@ def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, shape, opts
         ok, rows = True, 0
         for layer_no, sizes in enumerate(sizes_per_layer):
             h = torch.randn(sizes[rank], H, generator=cases.gen(100 * layer_no + rank)).to(dtype).cuda()
-            got = ep.layer(h, router, my_gu, my_dn)
+            x = torch.randn(h.shape, generator=cases.gen(7 + layer_no)).to(dtype).cuda() if opts.get("residual") else None
+            got = ep.layer(h, router, my_gu, my_dn, residual=x)
             srt = kernels.route_and_sort(h, r1, k, False, dbias)
             want = kernels._sorted_experts(h, srt, g1, d1, k, ep.mode)
+            if x is not None:
+                want = x + want  # the caller's own 16-bit addition
             torch.cuda.synchronize()
             ok = ok and torch.equal(got, want)
             rows += sizes[rank] * k
@@ -116,6 +119,11 @@ def test_one_rank_equals_the_single_gpu_layer(mode, dtype_name):
     run(1, [(1,), (7,), (0,), (200,), (64,), (333,)], mode, dtype_name)
 
 
+@pytest.mark.parametrize("dtype_name", ["float16", "bfloat16"])
+def test_one_rank_adds_the_residual_in_the_combine(dtype_name):
+    run(1, [(1,), (0,), (64,), (333,)], "gemv", dtype_name, residual=True)
+
+
 def test_one_rank_at_the_benchmark_shape():
     run(1, [(64,), (256,), (8,)], "gemv", shape=OLMOE, zipf=True)
     # compute shape: 300 tokens share tiles across senders; from 192 rows per expert and sender the
@@ -136,6 +144,11 @@ def test_two_ranks_bit_identical(mode):
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.skipif(n_gpus() < 2, reason="needs 2 GPUs")
+def test_two_ranks_add_the_residual_in_the_combine():
+    run(2, [(5, 9), (0, 3), (64, 64)], "gemv", residual=True)
+
+
 def test_two_ranks_bf16():
     run(2, [(33, 12), (12, 33)], "gemv", "bfloat16")
 

@@ -269,6 +269,29 @@ def test_combine_adds_in_expert_order(K, dtype, N, E, k, H):
     assert torch.equal(got.cpu(), mo.combine_expert_order(y, pos_of, idx, N))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("N,E,k,H", [(50, 16, 4, 24 * 8), (64, 64, 8, 2048), (1, 64, 8, 2048)])
+def test_combine_with_a_residual_is_the_separate_addition(K, dtype, N, E, k, H):
+    idx, w = cases.sort_inputs(E, k, N, 9)
+    counts, offsets, token, wsorted, pos_of = mo.sort_by_expert(idx, w, E)
+    y = torch.randn(N * k, H, generator=cases.gen(5)).to(dtype)
+    x = (torch.randn(N, H, generator=cases.gen(6)) * 3).to(dtype)
+    got = K.ext().combine(y.to(DEV), pos_of.to(DEV), idx.to(DEV), N, x.to(DEV))
+    assert torch.equal(got.cpu(), x + mo.combine_expert_order(y, pos_of, idx, N))  # two roundings, as the caller's add
+    with pytest.raises(RuntimeError):
+        K.ext().combine(y.to(DEV), pos_of.to(DEV), idx.to(DEV), N, x[:, :8].contiguous().to(DEV))
+
+
+@pytest.mark.parametrize("mode", ["gemv", "gemm"])
+def test_layer_with_a_residual_is_the_layer_plus_the_residual(K, mode):
+    spec = cases.LAYER_CASES["n64"]
+    h, router, gu, dn = (t.to(DEV) for t in cases.layer_inputs(**spec))
+    x = torch.randn(h.shape, generator=cases.gen(3)).to(h.dtype).to(DEV)
+    k = spec["k"]
+    assert torch.equal(K.moe_layer(h, router, gu, dn, k, False, mode, residual=x),
+                       x + K.moe_layer(h, router, gu, dn, k, False, mode))
+
+
 # ------------------------------------------------------------------------------ layer
 def layer_errors(K, h, router, gu, dn, mode, ridx, rw, want, loop16):
     got = K.experts(h.to(DEV), ridx.int().to(DEV), rw.to(DEV), gu.to(DEV), dn.to(DEV), mode).float().cpu()

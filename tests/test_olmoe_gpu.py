@@ -51,6 +51,20 @@ def test_graph_replay_equals_the_eager_decode_step():
     assert kernels.ext().device_status(DEV) == 0
 
 
+def test_residual_added_in_the_combine_gives_the_same_logits():
+    """Decoder(moe_adds_residual=True) hands x to the hook; moe_layer(residual=x) adds it in its
+    combine launch with the bits of the separate addition, so the whole model's logits agree."""
+    from switchyard_b200 import kernels
+    c, w, dec, olmoe = build(torch.float16, DEV, kernel_hook)
+    hook = lambda i, h, x: kernels.moe_layer(h, w["layers"][i]["router"], w["layers"][i]["gate_up"],
+                                             w["layers"][i]["down"], c.top_k, c.norm_topk_prob, "gemv", residual=x)
+    dec2 = olmoe.Decoder(c, w, hook, moe_adds_residual=True)
+    toks = torch.randint(3, c.vocab, (3, 11), generator=cases.gen(8)).to(DEV)
+    assert torch.equal(dec2.forward(toks), dec.forward(toks))
+    prompts = [torch.randint(3, c.vocab, (n,), generator=cases.gen(9)).tolist() for n in (5, 8)]
+    assert dec2.generate(prompts, 6, graph=False) == dec.generate(prompts, 6, graph=False)
+
+
 def test_fp16_model_on_the_gpu_is_close_to_float32_on_the_cpu():
     c, w16, dec16, olmoe = build(torch.float16, DEV, kernel_hook)
     w32 = {k: (v.float().cpu() if torch.is_tensor(v) else v) for k, v in w16.items() if k != "layers"}

@@ -83,3 +83,13 @@ def test_random_weights_are_the_same_on_every_rank():
     assert torch.equal(full["embed"], part["embed"]) and torch.equal(full["layers"][1]["wq"], part["layers"][1]["wq"])
     assert torch.equal(full["layers"][1]["gate_up"][4:], part["layers"][1]["gate_up"])
     assert torch.equal(full["layers"][0]["down"][4:], part["layers"][0]["down"])
+
+
+def test_a_hook_that_adds_the_residual_itself_gives_the_same_model():
+    hf, dec, olmoe = tiny()
+    dec2 = olmoe.Decoder(dec.c, dec.w, lambda i, h, x: x + dec.moe(i, h), moe_adds_residual=True)
+    t = torch.randint(3, 131, (2, 7), generator=torch.Generator().manual_seed(4))
+    assert torch.equal(dec2.forward(t), dec.forward(t))
+    cache, cache2 = (olmoe.Cache(dec.c, 2, 12, torch.float32, "cpu") for _ in range(2))
+    dec.forward(t[:, :6], cache), dec2.forward(t[:, :6], cache2)
+    assert torch.equal(dec2.decode_step(t[:, 6], cache2), dec.decode_step(t[:, 6], cache))
