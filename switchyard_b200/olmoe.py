@@ -281,6 +281,11 @@ class Decoder:
             nxt = logits.argmax(-1)
             out.append(nxt)
         result = torch.stack(out, 1).tolist()  # one transfer; also waits for the device
+        if dev.type == "cuda":
+            # a kernel of this request that gave up on a bounded wait (a peer that never arrived)
+            # has left garbage behind: raise instead of returning its tokens
+            from . import kernels
+            kernels.ext().check_device(dev)
         if marks is not None:
             marks.append(("decode_done", time.perf_counter()))
         return result

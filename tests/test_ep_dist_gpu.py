@@ -124,6 +124,17 @@ def test_one_rank_adds_the_residual_in_the_combine(dtype_name):
     run(1, [(1,), (0,), (64,), (333,)], "gemv", dtype_name, residual=True)
 
 
+def test_auto_mode_is_resolved_once_for_all_batch_sizes():
+    # mode="auto" is fixed from max_tokens, which every rank shares, so a layer with few tokens is
+    # computed in the same shape as one with many and equals the single-GPU layer of THAT mode
+    run(1, [(3,), (200,), (1,)], "auto")
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs 2 GPUs")
+def test_two_ranks_in_auto_mode_with_unequal_batches():
+    run(2, [(3, 200), (64, 1), (0, 130)], "auto")
+
+
 def test_one_rank_at_the_benchmark_shape():
     run(1, [(64,), (256,), (8,)], "gemv", shape=OLMOE, zipf=True)
     # compute shape: 300 tokens share tiles across senders; from 192 rows per expert and sender the
