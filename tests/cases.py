@@ -88,3 +88,46 @@ def capacity_inputs(seed=1):
     dn = torch.randn(EP_E, EP_H, EP_I, generator=g) * 0.3
     hs = [torch.randn(n, EP_H, generator=g) for n in (30, 17)]
     return router, gu, dn, hs
+
+
+def spawn_ranks(worker, world, args, limit=300):
+    """Runs worker(rank, world, *args, out) in `world` spawned processes and returns what they
+    put on `out`: one (rank, ok, detail) each, detail a string (a traceback) when the rank failed.
+    Never leaves a rank behind and never waits for one that cannot report: the children are
+    daemons, a rank that reports a failure or ends silently stops the wait for the others (they
+    may be waiting for it in a collective), and whatever is still alive afterwards is killed."""
+    import queue
+    import time
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=worker, args=(r, world) + tuple(args) + (out,), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    results, failed = [], False
+    deadline = time.monotonic() + limit
+    try:
+        while len(results) < world and not failed:
+            try:
+                results.append(out.get(timeout=1.0))
+                failed = isinstance(results[-1][2], str) and bool(results[-1][2])
+            except queue.Empty:
+                gone = [p for p in procs if p.exitcode is not None]
+                if len(gone) > len(results):  # a rank has ended without reporting (it could not even start)
+                    try:
+                        results.append(out.get(timeout=3.0))  # its report may still be on its way
+                        failed = isinstance(results[-1][2], str) and bool(results[-1][2])
+                    except queue.Empty:
+                        results.append((-1, False, f"a rank ended without a report (exit code {gone[0].exitcode})"))
+                        failed = True
+                elif time.monotonic() > deadline:
+                    results.append((-1, False, f"a rank did not report within {limit} s"))
+                    failed = True
+        for p in procs:
+            p.join(timeout=1 if failed else 30)
+    finally:
+        for p in procs:  # exactly the processes started above
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    return sorted(results, key=lambda r: r[0])

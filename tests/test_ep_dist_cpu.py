@@ -69,19 +69,11 @@ PLACEMENT = [5, 12, 0, 9, 3, 14, 7, 1, 10, 2, 15, 6, 11, 4, 13, 8]
                                                             (4, [(3, 7, 0, 2), (8, 8, 8, 8)], None, False),
                                                             (8, [(2, 0, 5, 1, 3, 4, 0, 6), (4,) * 8], None, False)])
 def test_protocol_over_gloo_processes(world, sizes, placement, residual):
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    out = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, sizes, placement, residual, out)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [out.get(timeout=180) for _ in procs]
-    for p in procs:
-        p.join(timeout=30)
-    for rank, ok, err in sorted(results):
+    results = cases.spawn_ranks(_rank_main, world, (_free_port(), sizes, placement, residual), limit=180)
+    for rank, ok, err in results:
         assert not err, f"rank {rank}:\n{err}"
         assert ok, f"rank {rank}: output differs from the one-process layer"
+    assert len(results) == world
 
 
 def test_window_layout_is_aligned_and_disjoint():

@@ -94,22 +94,12 @@ def _rank_main(rank, world, port, sizes_per_layer, mode, dtype_name, shape, opts
 
 
 def run(world, sizes_per_layer, mode, dtype_name="float16", shape=SMALL, **opts):
-    import torch.multiprocessing as mp
-    ctx = mp.get_context("spawn")
-    out = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, sizes_per_layer, mode, dtype_name, shape, opts, out))
-             for r in range(world)]
-    for p in procs:
-        p.start()
-    results = []
-    for _ in procs:
-        results.append(out.get(timeout=300))
-    for p in procs:
-        p.join(timeout=30)
-    for rank, ok, status in sorted(results, key=lambda r: r[0]):
+    assert world <= n_gpus(), f"{world} ranks need {world} GPUs"  # never start ranks that cannot get a device
+    results = cases.spawn_ranks(_worker, world, (_free_port(), sizes_per_layer, mode, dtype_name, shape, opts))
+    for rank, ok, status in results:
         assert status == 0, f"rank {rank}: {status}"  # a status code of a bounded wait, or a traceback
         assert ok, f"rank {rank}: output differs from the single-GPU layer"
+    assert len(results) == world
 
 
 # ---- one rank: the whole transport on a single GPU
@@ -130,7 +120,7 @@ def test_auto_mode_is_resolved_once_for_all_batch_sizes():
     run(1, [(3,), (200,), (1,)], "auto")
 
 
-@pytest.mark.skipif(n_gpus() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
 def test_two_ranks_in_auto_mode_with_unequal_batches():
     run(2, [(3, 200), (64, 1), (0, 130)], "auto")
 
@@ -155,11 +145,11 @@ def test_two_ranks_bit_identical(mode):
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
-@pytest.mark.skipif(n_gpus() < 2, reason="needs 2 GPUs")
 def test_two_ranks_add_the_residual_in_the_combine():
     run(2, [(5, 9), (0, 3), (64, 64)], "gemv", residual=True)
 
 
+@pytest.mark.skipif(n_gpus() < 2, reason="needs two GPUs")
 def test_two_ranks_bf16():
     run(2, [(33, 12), (12, 33)], "gemv", "bfloat16")
 
