@@ -13,6 +13,16 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA GPU (run with -m gpu on a B200)")
 
 
+def pytest_collection_modifyitems(config, items):
+    # no test may wait for ever (a rank that never reports, a peer that never arrives): with the
+    # pytest-timeout plugin present every test gets a limit, a test's own mark wins
+    if not config.pluginmanager.hasplugin("timeout"):
+        return
+    for item in items:
+        if item.get_closest_marker("timeout") is None:
+            item.add_marker(pytest.mark.timeout(600))
+
+
 @pytest.fixture(scope="session")
 def golden():
     import numpy as np
