@@ -216,7 +216,7 @@ int sy_combine(const void* y, const int32_t* pos_of, const int32_t* idx, int n_t
 /* combine_add — sy_combine followed by the caller's residual add (switchyard/model.py:135,
  * `x = x + self.moe(i, h)`) in the same launch: out[t, :] = round16( float(residual[t, :]) +
  * float(round16(sum)) ), the bits of the 16-bit addition done separately. residual 16-bit
- * [n_tokens, hidden], 16-byte aligned; out may be residual itself. */
+ * [n_tokens, hidden], 16-byte aligned; out must not overlap residual or y. */
 int sy_combine_add(const void* y, const int32_t* pos_of, const int32_t* idx, int n_tokens, int top_k, int hidden,
                    const void* residual, void* out, int dtype, void* stream);
 
