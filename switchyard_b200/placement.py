@@ -40,7 +40,8 @@ def imbalance(rows):
 
 def balanced(load, ranks, sweeps=8):
     """A placement with E/R experts per rank whose busiest rank is as light as a greedy deal
-    plus pairwise swaps can make it. load: per-expert rows (any sequence or tensor)."""
+    plus pairwise swaps can make it, and never heavier than with contiguous blocks. load:
+    per-expert rows (any sequence or tensor)."""
     load = [float(x) for x in torch.as_tensor(load, dtype=torch.float64).tolist()]
     E = len(load)
     assert E % ranks == 0, "experts must split evenly over the ranks"
@@ -75,7 +76,12 @@ def balanced(load, ranks, sweeps=8):
         held[other][held[other].index(b)] = a
         weight[top] += load[b] - load[a]
         weight[other] += load[a] - load[b]
-    return [e for r in range(ranks) for e in sorted(held[r])]
+    placement = [e for r in range(ranks) for e in sorted(held[r])]
+    # never hand back something worse than the default: on a load that happens to suit the
+    # contiguous blocks the deal can end above them
+    if max(weight) > rank_rows(load, contiguous(E), ranks).max().item() + 1e-9:
+        return contiguous(E)
+    return placement
 
 
 class LoadMeter:

@@ -50,3 +50,22 @@ def test_load_meter_accumulates():
     assert m.read() == [1, 5, 2, 0]
     m.reset()
     assert m.read() == [0, 0, 0, 0]
+
+
+def test_properties_on_random_loads():
+    """Whatever the load: a permutation with E/R experts per rank, never heavier than contiguous
+    blocks, every row accounted for."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.sampled_from([2, 4, 8]), st.integers(1, 4), st.data())
+    def check(ranks, per, data):
+        E = ranks * per
+        load = data.draw(st.lists(st.integers(0, 5000), min_size=E, max_size=E))
+        got = pl.balanced(load, ranks)
+        assert sorted(got) == list(range(E))
+        rows = pl.rank_rows(load, got, ranks)
+        assert rows.max().item() <= pl.rank_rows(load, pl.contiguous(E), ranks).max().item() + 1e-9
+        assert rows.sum().item() == float(sum(load))
+
+    check()
